@@ -1,0 +1,394 @@
+"""Host-side mirror of the reference crate's SM100 operator surface, over the C-ABI library.
+
+Names, argument meaning and error behaviour follow deepgemm/src/ops_sm100.rs,
+deepgemm/src/heuristics_sm100.rs, deepgemm/src/types.rs and deepgemm/src/device.rs of
+idrees2516/deepgemm-rust.  Every compute call goes through libdgb200.so (hand-written sm_100a
+kernels); torch is used only to own device memory and streams.  There is no CPU path: importing
+works anywhere, but creating a DgContext needs a B200.
+"""
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libdgb200.so")
+INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
+
+
+class DgError(RuntimeError):
+    """deepgemm/src/types.rs:9-21 (DgError); .kind is one of Driver, Shape, Unsupported, Timeout."""
+
+    KINDS = {1: "Driver", 2: "Shape", 3: "Unsupported", 4: "Timeout"}
+
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.kind = self.KINDS.get(code, "Unknown")
+        super().__init__(f"{self.kind}: {message}")
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python -m deepgemm_rust_b200.build` "
+            "(nvcc, sm_100a). There is no fallback implementation.")
+    return C.CDLL(_LIB_PATH)
+
+
+_lib = _load()
+
+
+class _LpOperand(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("sf", C.c_void_p), ("rows", C.c_uint32), ("k", C.c_uint32), ("ld", C.c_uint32),
+                ("bits", C.c_uint32), ("gran_k", C.c_uint32), ("major_mn", C.c_uint32), ("data_len", C.c_size_t),
+                ("sf_len", C.c_size_t)]
+
+
+class _Out(C.Structure):
+    _fields_ = [("kind", C.c_int), ("buf", C.c_void_p), ("ld", C.c_uint32), ("sfd", C.c_void_p), ("buf_len", C.c_size_t),
+                ("sfd_len", C.c_size_t)]
+
+
+class _Epilogue(C.Structure):
+    _fields_ = [("alpha", C.c_float), ("has_alpha", C.c_int), ("accumulate", C.c_int), ("tc_util", C.c_uint32)]
+
+
+class _Desc(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("gemm_type", "m", "n", "k", "num_groups", "expected_m", "a_bits", "b_bits", "gran_a",
+                                          "gran_b", "cd_dtype", "num_sms")]
+
+
+class _Config(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("swap_ab", "block_m", "block_n", "block_k", "cluster_m", "cluster_n", "num_stages",
+                                          "num_accum_stages", "smem_size", "num_tiles")]
+
+
+def _proto(name, restype, *argtypes):
+    f = getattr(_lib, name)
+    f.restype = restype
+    f.argtypes = list(argtypes)
+    return f
+
+
+_vp, _u32, _sz = C.c_void_p, C.c_uint32, C.c_size_t
+_lib.dg_last_error.restype = C.c_char_p
+_ctx_create = _proto("dg_ctx_create", C.c_int, C.c_int, C.POINTER(_vp))
+_ctx_create_on_stream = _proto("dg_ctx_create_on_stream", C.c_int, C.c_int, _vp, C.POINTER(_vp))
+_ctx_destroy = _proto("dg_ctx_destroy", C.c_int, _vp)
+_ctx_sync = _proto("dg_ctx_sync", C.c_int, _vp)
+_ctx_num_sms = _proto("dg_ctx_num_sms", C.c_int, _vp, C.POINTER(C.c_int))
+_ctx_stream = _proto("dg_ctx_stream", _vp, _vp)
+_ctx_set_stream = _proto("dg_ctx_set_stream", C.c_int, _vp, _vp)
+_ctx_check_status = _proto("dg_ctx_check_status", C.c_int, _vp)
+_gemm = _proto("dg_fp8_fp4_gemm", C.c_int, _vp, C.POINTER(_LpOperand), C.POINTER(_LpOperand), C.POINTER(_Out), C.POINTER(_Epilogue))
+_gemm_contig = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous", C.c_int, _vp, C.POINTER(_LpOperand), _vp, C.POINTER(_LpOperand),
+                      C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_gemm_contig_ends = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_ends", C.c_int, _vp, C.POINTER(_LpOperand), _vp,
+                           C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_gemm_masked = _proto("dg_m_grouped_fp8_fp4_gemm_masked", C.c_int, _vp, C.POINTER(_LpOperand), _vp, C.POINTER(_LpOperand),
+                      C.POINTER(_Out), _u32, _u32, C.POINTER(_Epilogue))
+_bmm = _proto("dg_fp8_fp4_bmm", C.c_int, _vp, C.POINTER(_LpOperand), C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_sf_packed_cols = _proto("dg_sf_packed_cols", _u32, _u32, _u32)
+_sf_aligned_rows = _proto("dg_sf_aligned_rows", _u32, _u32)
+_sf_words = _proto("dg_sf_words", _sz, _u32, _u32, _u32, _u32)
+_cast_fp8 = _proto("dg_cast_bf16_to_fp8_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp)
+_cast_fp4 = _proto("dg_cast_bf16_to_fp4_packed_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, C.c_int, _vp, _vp)
+_transform_sf = _proto("dg_transform_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _vp)
+_tsf1d = _proto("dg_transform_sf1d_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp)
+_tsf2d = _proto("dg_transform_sf2d_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _vp)
+_tsft = _proto("dg_transform_sf_t_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _vp)
+_group_ends = _proto("dg_group_ends_from_m_indices", C.c_int, _vp, _vp, _u32, _u32, _vp)
+_unpack_fp4 = _proto("dg_unpack_fp4_raw", C.c_int, _vp, _vp, _sz, _vp)
+_set_mk = _proto("dg_set_mk_alignment_for_contiguous_layout", C.c_int, _u32)
+_get_mk = _proto("dg_get_mk_alignment_for_contiguous_layout", _u32)
+_get_mk_theory = _proto("dg_get_theoretical_mk_alignment_for_contiguous_layout", _u32, _u32)
+_best_config = _proto("dg_best_config", C.c_int, C.POINTER(_Desc), C.POINTER(_Config))
+
+SF_RULE_REFERENCE_CPU = 0
+SF_RULE_RANGE_FIT = 1
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise DgError(rc, (_lib.dg_last_error() or b"").decode())
+
+
+class GemmType:
+    """deepgemm/src/types.rs:27-38"""
+    Normal = 0
+    MGroupedContiguous = 1
+    MGroupedMasked = 2
+    Batched = 3
+
+
+class DgContext:
+    """deepgemm/src/device.rs:40-56: one device, one stream.  By default the context adopts the
+    current torch stream of that device, so tensors produced by torch are ordered with the kernels."""
+
+    def __init__(self, ordinal: int = 0, stream: Optional[int] = None, own_stream: bool = False):
+        self._h = _vp()
+        self.ordinal = ordinal
+        if own_stream:
+            _check(_ctx_create(ordinal, C.byref(self._h)))
+        else:
+            if stream is None:
+                if not torch.cuda.is_available():
+                    raise DgError(1, "no CUDA device available; this library has no CPU path")
+                stream = torch.cuda.current_stream(ordinal).cuda_stream
+            _check(_ctx_create_on_stream(ordinal, _vp(stream), C.byref(self._h)))
+
+    @classmethod
+    def new(cls, ordinal: int = 0) -> "DgContext":
+        return cls(ordinal)
+
+    def sync(self):
+        """device.rs:129; raises DgError(Timeout) if a kernel gave up on a device-side wait."""
+        _check(_ctx_sync(self._h))
+
+    def num_sms(self) -> int:
+        n = C.c_int()
+        _check(_ctx_num_sms(self._h, C.byref(n)))
+        return n.value
+
+    @property
+    def stream(self) -> int:
+        return _ctx_stream(self._h) or 0
+
+    def set_stream(self, cuda_stream: int):
+        _check(_ctx_set_stream(self._h, _vp(cuda_stream)))
+
+    def close(self):
+        if self._h:
+            _ctx_destroy(self._h)
+            self._h = _vp()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class LpOperand:
+    """ops_sm100.rs:33-45.  data: uint8 tensor; sf: int32 tensor holding the packed UE8M0 words."""
+    data: torch.Tensor
+    sf: torch.Tensor
+    rows: int
+    k: int
+    ld: int
+    bits: int = 8
+    gran_k: int = 128
+    major_mn: bool = False
+
+    def _c(self) -> _LpOperand:
+        return _LpOperand(self.data.data_ptr(), self.sf.data_ptr(), self.rows, self.k, self.ld, self.bits, self.gran_k,
+                          1 if self.major_mn else 0, self.data.numel() * self.data.element_size(), self.sf.numel())
+
+
+@dataclass
+class Sm100Out:
+    """ops_sm100.rs:95-110.  kind 0 = bf16, 1 = f32, 2 = e4m3 with per-row per-32-column UE8M0 scales."""
+    kind: int
+    buf: torch.Tensor
+    ld: int
+    sfd: Optional[torch.Tensor] = None
+
+    @classmethod
+    def Bf16(cls, buf, ld):
+        return cls(0, buf, ld)
+
+    @classmethod
+    def F32(cls, buf, ld):
+        return cls(1, buf, ld)
+
+    @classmethod
+    def Fp8(cls, buf, ld, sfd):
+        return cls(2, buf, ld, sfd)
+
+    def _c(self) -> _Out:
+        return _Out(self.kind, self.buf.data_ptr(), self.ld, self.sfd.data_ptr() if self.sfd is not None else None,
+                    self.buf.numel(), self.sfd.numel() if self.sfd is not None else 0)
+
+
+@dataclass
+class Sm100Epilogue:
+    """ops_sm100.rs:114-131"""
+    alpha: Optional[float] = None
+    accumulate: bool = False
+    tc_util: int = 100
+
+    def _c(self) -> _Epilogue:
+        return _Epilogue(self.alpha if self.alpha is not None else 1.0, 1 if self.alpha is not None else 0,
+                         1 if self.accumulate else 0, self.tc_util)
+
+
+def _epi(epi):
+    return (epi or Sm100Epilogue())._c()
+
+
+def fp8_fp4_gemm_dev(ctx: DgContext, a: LpOperand, b: LpOperand, out: Sm100Out, epi: Optional[Sm100Epilogue] = None):
+    """ops_sm100.rs:719"""
+    ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
+    _check(_gemm(ctx._h, C.byref(ca), C.byref(cb), C.byref(co), C.byref(ce)))
+
+
+def m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, m_indices: torch.Tensor, b, out, num_groups: int, epi=None):
+    """ops_sm100.rs:759; b.rows = num_groups * n."""
+    ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
+    _check(_gemm_contig(ctx._h, C.byref(ca), _vp(m_indices.data_ptr()), C.byref(cb), C.byref(co), num_groups, C.byref(ce)))
+
+
+def m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a, group_ends: torch.Tensor, b, out, num_groups: int, epi=None):
+    """Same GEMM from a prebuilt group-end table (see psum_from_m_indices_dev)."""
+    ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
+    _check(_gemm_contig_ends(ctx._h, C.byref(ca), _vp(group_ends.data_ptr()), C.byref(cb), C.byref(co), num_groups, C.byref(ce)))
+
+
+def m_grouped_fp8_fp4_gemm_masked_dev(ctx, a, masked_m: torch.Tensor, b, out, num_groups: int, expected_m: int, epi=None):
+    """ops_sm100.rs:815; a.rows = m_max, b.rows = num_groups * n."""
+    ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
+    _check(_gemm_masked(ctx._h, C.byref(ca), _vp(masked_m.data_ptr()), C.byref(cb), C.byref(co), num_groups, expected_m, C.byref(ce)))
+
+
+def fp8_fp4_bmm_dev(ctx, a, b, out, num_groups: int, epi=None):
+    """ops_sm100.rs:864; a.rows = m and b.rows = n per group."""
+    ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
+    _check(_bmm(ctx._h, C.byref(ca), C.byref(cb), C.byref(co), num_groups, C.byref(ce)))
+
+
+def sf_packed_cols(k: int, gran_k: int) -> int:
+    """ops_sm100.rs:1091"""
+    return _sf_packed_cols(k, gran_k)
+
+
+def sf_aligned_rows(rows: int) -> int:
+    """ops_sm100.rs:1096"""
+    return _sf_aligned_rows(rows)
+
+
+def alloc_sf(ctx: DgContext, rows: int, k: int, gran_k: int, num_groups: int = 1) -> torch.Tensor:
+    """ops_sm100.rs:1107: zero-initialised packed scale buffer (int32 words)."""
+    return torch.zeros(_sf_words(rows, k, gran_k, max(num_groups, 1)), dtype=torch.int32, device=f"cuda:{ctx.ordinal}")
+
+
+def cast_bf16_to_fp8_sf_dev(ctx, src: torch.Tensor, src_ld: int, rows: int, k: int, gran_k: int, num_groups: int = 1
+                            ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """ops_sm100.rs:1186: bf16 -> (e4m3 bytes (rows, k), packed UE8M0 words)."""
+    dst = torch.empty((rows, k), dtype=torch.uint8, device=src.device)
+    sf = alloc_sf(ctx, rows, k, gran_k, num_groups)
+    _check(_cast_fp8(ctx._h, _vp(src.data_ptr()), src_ld, rows, k, gran_k, num_groups, _vp(dst.data_ptr()), _vp(sf.data_ptr())))
+    return dst, sf
+
+
+def cast_bf16_to_fp4_packed_sf_dev(ctx, src: torch.Tensor, src_ld: int, rows: int, k: int, num_groups: int = 1,
+                                   sf_rule: int = SF_RULE_REFERENCE_CPU) -> Tuple[torch.Tensor, torch.Tensor]:
+    """ops_sm100.rs:1135: bf16 -> (packed e2m1 (rows, k/2), packed per-32 UE8M0 words)."""
+    dst = torch.empty((rows, k // 2), dtype=torch.uint8, device=src.device)
+    sf = alloc_sf(ctx, rows, k, 32, num_groups)
+    _check(_cast_fp4(ctx._h, _vp(src.data_ptr()), src_ld, rows, k, num_groups, sf_rule, _vp(dst.data_ptr()), _vp(sf.data_ptr())))
+    return dst, sf
+
+
+def transform_sf_dev(ctx, sf: torch.Tensor, mn: int, sf_k: int, num_batches: int = 1) -> torch.Tensor:
+    """deepgemm/src/ops.rs:52: (batches, mn, sf_k) f32 -> (batches*sf_k, align4(mn)) f32."""
+    dst = torch.empty((num_batches * sf_k, sf_aligned_rows(mn)), dtype=torch.float32, device=sf.device)
+    _check(_transform_sf(ctx._h, _vp(sf.data_ptr()), mn, sf_k, num_batches, _vp(dst.data_ptr())))
+    return dst
+
+
+def transform_sf1d_packed_ue8m0_dev(ctx, src, src_ld, rows, k, gran_k, num_groups=1) -> torch.Tensor:
+    """ops_sm100.rs:1250"""
+    dst = alloc_sf(ctx, rows, k, gran_k, num_groups)
+    _check(_tsf1d(ctx._h, _vp(src.data_ptr()), src_ld, rows, k, gran_k, num_groups, _vp(dst.data_ptr())))
+    return dst
+
+
+def transform_sf2d_packed_ue8m0_dev(ctx, src, src_ld, rows, k, num_groups=1) -> torch.Tensor:
+    """ops_sm100.rs:1294"""
+    dst = alloc_sf(ctx, rows, k, 128, num_groups)
+    _check(_tsf2d(ctx._h, _vp(src.data_ptr()), src_ld, rows, k, num_groups, _vp(dst.data_ptr())))
+    return dst
+
+
+def transform_sf_t_packed_ue8m0_dev(ctx, src, rows, k, gran_k, num_groups=1) -> torch.Tensor:
+    """ops_sm100.rs:1372"""
+    dst = alloc_sf(ctx, rows, k, gran_k, num_groups)
+    _check(_tsft(ctx._h, _vp(src.data_ptr()), rows, k, gran_k, num_groups, _vp(dst.data_ptr())))
+    return dst
+
+
+def psum_from_m_indices_dev(ctx, m_indices: torch.Tensor, num_groups: int) -> torch.Tensor:
+    """ops_sm100.rs:1073: one-past-the-last row of every group (int32 words)."""
+    out = torch.empty(num_groups, dtype=torch.int32, device=m_indices.device)
+    _check(_group_ends(ctx._h, _vp(m_indices.data_ptr()), m_indices.numel(), num_groups, _vp(out.data_ptr())))
+    return out
+
+
+def unpack_fp4_raw_dev(ctx, src: torch.Tensor, packed_len: int) -> torch.Tensor:
+    """ops_sm100.rs:1338"""
+    dst = torch.empty(packed_len * 2, dtype=torch.uint8, device=src.device)
+    _check(_unpack_fp4(ctx._h, _vp(src.data_ptr()), packed_len, _vp(dst.data_ptr())))
+    return dst
+
+
+def set_mk_alignment_for_contiguous_layout(value: int):
+    """types.rs:195 (raises instead of panicking on a bad value)."""
+    _check(_set_mk(value))
+
+
+def get_mk_alignment_for_contiguous_layout() -> int:
+    """types.rs:204"""
+    return _get_mk()
+
+
+def get_theoretical_mk_alignment_for_contiguous_layout(arch_major: int) -> int:
+    """types.rs:213"""
+    return _get_mk_theory(arch_major)
+
+
+@dataclass
+class Sm100Desc:
+    """heuristics_sm100.rs:61-87 (fields this build's tile choice reads)."""
+    gemm_type: int
+    m: int
+    n: int
+    k: int
+    num_groups: int = 1
+    expected_m: int = 0
+    a_bits: int = 8
+    b_bits: int = 8
+    gran_a: int = 128
+    gran_b: int = 128
+    cd_dtype: int = 0
+    num_sms: int = 148
+
+
+@dataclass
+class Sm100Config:
+    """heuristics_sm100.rs:17-57 flattened."""
+    swap_ab: bool
+    block_m: int
+    block_n: int
+    block_k: int
+    cluster_m: int
+    cluster_n: int
+    num_stages: int
+    num_accum_stages: int
+    smem_size: int
+    num_tiles: int
+
+
+SM100_SMEM_CAPACITY = 232448
+
+
+def best_config(desc: Sm100Desc) -> Sm100Config:
+    """heuristics_sm100.rs:455"""
+    d = _Desc(desc.gemm_type, desc.m, desc.n, desc.k, desc.num_groups, desc.expected_m or desc.m, desc.a_bits, desc.b_bits,
+              desc.gran_a, desc.gran_b, desc.cd_dtype, desc.num_sms)
+    c = _Config()
+    _check(_best_config(C.byref(d), C.byref(c)))
+    return Sm100Config(bool(c.swap_ab), c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n, c.num_stages,
+                       c.num_accum_stages, c.smem_size, c.num_tiles)

@@ -1,0 +1,36 @@
+"""Ahead-of-time build of libdgb200.so (the C-ABI library) with nvcc for sm_100a.
+
+`python -m deepgemm_rust_b200.build` (or build()) compiles csrc/dg_api.cu, which includes the
+kernel headers, into deepgemm_rust_b200/libdgb200.so.  nvcc cross-compiles without a GPU.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUT = os.path.join(HERE, "libdgb200.so")
+SOURCES = ["dg_api.cu"]
+DEPS = ["dg_api.cu", "dg_gemm_kernel.cuh", "dg_cast_kernels.cuh", "dg_ptx.cuh", os.path.join("..", "..", "include", "dgb200.h")]
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+         "-Xcompiler", "-fPIC,-fvisibility=default", "--expt-relaxed-constexpr"]
+
+
+def needs_build() -> bool:
+    if not os.path.exists(OUT):
+        return True
+    t = os.path.getmtime(OUT)
+    return any(os.path.getmtime(os.path.join(CSRC, d)) > t for d in DEPS)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not needs_build():
+        return OUT
+    cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUT] + [os.path.join(CSRC, s) for s in SOURCES]
+    subprocess.check_call(cmd)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,587 @@
+// Host side of the C ABI declared in include/dgb200.h: context, argument validation, tile
+// configuration, tensor-map encoding and kernel launches.  No CPU compute path exists here:
+// every entry point either launches sm_100a kernels or returns an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/dgb200.h"
+#include "dg_cast_kernels.cuh"
+#include "dg_gemm_kernel.cuh"
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define DG_CUDA(expr)                                                                            \
+    do {                                                                                         \
+        cudaError_t e_ = (expr);                                                                 \
+        if (e_ != cudaSuccess) return fail(DG_ERR_DRIVER, "%s: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+std::atomic<uint32_t> g_mk_alignment{128};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+constexpr uint32_t kSmemCapacity = 232448;  // 227 KB opt-in maximum per CTA on sm_100
+
+uint32_t align4(uint32_t x) { return (x + 3) / 4 * 4; }
+uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+struct dg_ctx {
+    int ordinal = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int num_sms = 0;
+    dg::Status* status = nullptr;       // device word block the kernels report into
+    uint32_t* group_ends = nullptr;     // scratch for the contiguous layout's group-end table
+    uint32_t group_ends_cap = 0;
+};
+
+extern "C" {
+
+const char* dg_last_error(void) { return g_last_error.c_str(); }
+
+static int ctx_create(int ordinal, void* stream, bool adopt, dg_ctx** out) {
+    if (out == nullptr) return fail(DG_ERR_SHAPE, "null output pointer");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail(DG_ERR_DRIVER, "no CUDA device available (%s); this library has no CPU path", cudaGetErrorString(e));
+    if (ordinal < 0 || ordinal >= count) return fail(DG_ERR_SHAPE, "device ordinal %d out of range (0..%d)", ordinal, count - 1);
+    DG_CUDA(cudaSetDevice(ordinal));
+    cudaDeviceProp prop;
+    DG_CUDA(cudaGetDeviceProperties(&prop, ordinal));
+    if (prop.major != 10)
+        return fail(DG_ERR_UNSUPPORTED, "device %d is sm_%d%d; these kernels are built for sm_100a only", ordinal, prop.major, prop.minor);
+    if (encode_tiled_fn() == nullptr) return fail(DG_ERR_DRIVER, "cuTensorMapEncodeTiled not found in the driver");
+    dg_ctx* c = new dg_ctx();
+    c->ordinal = ordinal;
+    c->num_sms = prop.multiProcessorCount;
+    if (adopt) {
+        c->stream = static_cast<cudaStream_t>(stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { delete c; return fail(DG_ERR_DRIVER, "cudaStreamCreate failed"); }
+        c->owns_stream = true;
+    }
+    if (cudaMalloc(&c->status, sizeof(dg::Status)) != cudaSuccess || cudaMemset(c->status, 0, sizeof(dg::Status)) != cudaSuccess) {
+        delete c;
+        return fail(DG_ERR_DRIVER, "allocating the device status word failed");
+    }
+    *out = c;
+    return DG_OK;
+}
+
+int dg_ctx_create(int ordinal, dg_ctx** out) { return ctx_create(ordinal, nullptr, false, out); }
+int dg_ctx_create_on_stream(int ordinal, void* cuda_stream, dg_ctx** out) { return ctx_create(ordinal, cuda_stream, true, out); }
+
+int dg_ctx_destroy(dg_ctx* ctx) {
+    if (ctx == nullptr) return DG_OK;
+    cudaSetDevice(ctx->ordinal);
+    if (ctx->status) cudaFree(ctx->status);
+    if (ctx->group_ends) cudaFree(ctx->group_ends);
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return DG_OK;
+}
+
+int dg_ctx_check_status(dg_ctx* ctx) {
+    if (ctx == nullptr) return fail(DG_ERR_SHAPE, "null context");
+    dg::Status st;
+    DG_CUDA(cudaMemcpy(&st, ctx->status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st.code != 0) {
+        cudaMemset(ctx->status, 0, sizeof(st));
+        return fail(DG_ERR_TIMEOUT, "a device-side wait ran out: block %u, site 0x%x, parity %u", st.block, st.site, st.extra);
+    }
+    return DG_OK;
+}
+
+int dg_ctx_sync(dg_ctx* ctx) {
+    if (ctx == nullptr) return fail(DG_ERR_SHAPE, "null context");
+    DG_CUDA(cudaStreamSynchronize(ctx->stream));
+    return dg_ctx_check_status(ctx);
+}
+
+int dg_ctx_num_sms(const dg_ctx* ctx, int* out) {
+    if (ctx == nullptr || out == nullptr) return fail(DG_ERR_SHAPE, "null argument");
+    *out = ctx->num_sms;
+    return DG_OK;
+}
+void* dg_ctx_stream(const dg_ctx* ctx) { return ctx ? ctx->stream : nullptr; }
+int dg_ctx_set_stream(dg_ctx* ctx, void* cuda_stream) {
+    if (ctx == nullptr) return fail(DG_ERR_SHAPE, "null context");
+    if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    ctx->owns_stream = false;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);
+    return DG_OK;
+}
+
+// ------------------------------------------------------------------ size helpers / knobs
+uint32_t dg_sf_packed_cols(uint32_t k, uint32_t gran_k) { return gran_k ? ceil_div(k, gran_k * 4) : 0; }
+uint32_t dg_sf_aligned_rows(uint32_t rows) { return align4(rows); }
+size_t dg_sf_words(uint32_t rows, uint32_t k, uint32_t gran_k, uint32_t num_groups) {
+    const uint32_t g = num_groups ? num_groups : 1;
+    return static_cast<size_t>(dg_sf_packed_cols(k, gran_k)) * g * align4(rows / g);
+}
+
+int dg_set_mk_alignment_for_contiguous_layout(uint32_t value) {
+    if (value < 16 || value > 256 || (value & (value - 1)) != 0)
+        return fail(DG_ERR_SHAPE, "mk alignment must be a power of two in [16, 256], got %u", value);
+    g_mk_alignment.store(value);
+    return DG_OK;
+}
+uint32_t dg_get_mk_alignment_for_contiguous_layout(void) { return g_mk_alignment.load(); }
+uint32_t dg_get_theoretical_mk_alignment_for_contiguous_layout(uint32_t arch_major) { return arch_major == 10 ? 256u : 128u; }
+
+// ------------------------------------------------------------------------- heuristics
+// Tile choice for 148 SMs / 227 KB shared memory / 512 TMEM columns.  A rows always ride the
+// UMMA M dimension (128 per tile); BLOCK_N is picked from the widths the epilogue of the output
+// type can store, minimising waves x per-tile cost; stages fill the shared memory left over.
+int dg_best_config(const dg_desc* d, dg_config* out) {
+    if (d == nullptr || out == nullptr) return fail(DG_ERR_SHAPE, "null argument");
+    if ((d->a_bits != 8 && d->a_bits != 4) || (d->b_bits != 8 && d->b_bits != 4)) return fail(DG_ERR_SHAPE, "operand bits must be 8 or 4");
+    if (d->a_bits != d->b_bits) return fail(DG_ERR_UNSUPPORTED, "mixed FP8 x FP4 operands are not built yet");
+    const bool mxf4 = d->a_bits == 4;
+    const uint32_t block_k = mxf4 ? 256 : 128;
+    const uint32_t sms = d->num_sms ? d->num_sms : 148;
+    const uint32_t groups = d->num_groups ? d->num_groups : 1;
+    const uint32_t sfa_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
+    const uint32_t sfb_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
+    const uint32_t step = d->cd_dtype == DG_OUT_FP8 ? 128 : (d->cd_dtype == DG_OUT_F32 ? 32 : 64);
+    uint32_t m_blocks;
+    if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) m_blocks = ceil_div(d->m, 128);
+    else if (d->gemm_type == DG_GEMM_M_GROUPED_MASKED) m_blocks = groups * ceil_div(d->expected_m ? d->expected_m : d->m, 128);
+    else m_blocks = groups * ceil_div(d->m, 128);
+
+    uint32_t best_n = 0, best_accum = 0, best_tiles = 0;
+    double best_cost = 0;
+    const char* force = getenv("DG_BLOCK_N");
+    for (uint32_t bn = step; bn <= 256; bn += step) {
+        if (bn % 16 != 0) continue;
+        if (force && static_cast<uint32_t>(atoi(force)) != bn) continue;
+        const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
+        const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
+        if (bn + sf_cols > 512) continue;
+        const uint32_t tiles = m_blocks * ceil_div(d->n, bn);
+        const uint32_t waves = ceil_div(tiles, sms);
+        // per-tile time ~ the wider of the MMA (bn) and the shared-memory traffic of the A tile (~ 96),
+        // plus the part of the epilogue that cannot hide behind the next tile
+        const double k_blocks = ceil_div(d->k, block_k);
+        const double tile_cost = k_blocks * (bn > 96 ? bn : 96) + (accum == 1 ? 6.0 * bn : 0.5 * bn) + 300.0;
+        const double cost = waves * tile_cost;
+        if (best_n == 0 || cost < best_cost - 1e-9) { best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; }
+    }
+    if (best_n == 0) return fail(DG_ERR_SHAPE, "no tile configuration fits (DG_BLOCK_N=%s)", force ? force : "");
+    uint32_t stages = dg::kMaxStages;
+    const char* force_stages = getenv("DG_STAGES");
+    if (force_stages) stages = static_cast<uint32_t>(atoi(force_stages));
+    while (stages > 1 && dg::gemm_smem_bytes(best_n, stages, sfa_words, sfb_words) > kSmemCapacity) --stages;
+    if (stages < 1 || stages > dg::kMaxStages || dg::gemm_smem_bytes(best_n, stages, sfa_words, sfb_words) > kSmemCapacity)
+        return fail(DG_ERR_SHAPE, "no pipeline depth fits in shared memory");
+    out->swap_ab = 0;
+    out->block_m = 128;
+    out->block_n = best_n;
+    out->block_k = block_k;
+    out->cluster_m = 1;
+    out->cluster_n = 1;
+    out->num_stages = stages;
+    out->num_accum_stages = best_accum;
+    out->smem_size = dg::gemm_smem_bytes(best_n, stages, sfa_words, sfb_words);
+    out->num_tiles = best_tiles;
+    return DG_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+// ----------------------------------------------------------------------- tensor maps
+int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base, const uint64_t* dims,
+               const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle, const char* what) {
+    cuuint64_t gdim[3], gstride[2];
+    cuuint32_t gbox[3], estride[3] = {1, 1, 1};
+    for (uint32_t i = 0; i < rank; ++i) { gdim[i] = dims[i]; gbox[i] = box[i]; }
+    for (uint32_t i = 0; i + 1 < rank; ++i) gstride[i] = strides_bytes[i];
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return fail(DG_ERR_SHAPE, "%s: base address must be 16-byte aligned", what);
+    for (uint32_t i = 0; i + 1 < rank; ++i)
+        if (gstride[i] % 16 != 0) return fail(DG_ERR_SHAPE, "%s: stride %llu bytes is not a multiple of 16", what, (unsigned long long)gstride[i]);
+    CUresult r = encode_tiled_fn()(map, dtype, rank, const_cast<void*>(base), gdim, gstride, gbox, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DG_ERR_DRIVER, "cuTensorMapEncodeTiled(%s) failed with %d", what, static_cast<int>(r));
+    return DG_OK;
+}
+
+int check_operand(const dg_lp_operand* op, const char* name, uint32_t total_rows, uint32_t groups) {
+    if (op == nullptr || op->data == nullptr || op->sf == nullptr) return fail(DG_ERR_SHAPE, "%s: null operand", name);
+    if (op->bits != 8 && op->bits != 4) return fail(DG_ERR_SHAPE, "invalid bits %u", op->bits);
+    if (op->gran_k != 32 && op->gran_k != 128) return fail(DG_ERR_SHAPE, "invalid gran_k %u", op->gran_k);
+    if (op->major_mn) return fail(op->bits == 4 ? DG_ERR_SHAPE : DG_ERR_UNSUPPORTED, "%s: only K-major operands are supported", name);
+    if (op->bits == 4 && (op->k % 128 != 0 || op->ld % 128 != 0)) return fail(DG_ERR_SHAPE, "FP4 k and ld must be multiples of 128");
+    if (op->bits == 4 && op->gran_k != 32) return fail(DG_ERR_UNSUPPORTED, "FP4 operands need gran_k = 32");
+    if (op->k == 0 || op->k % op->gran_k != 0) return fail(DG_ERR_SHAPE, "k (%u) must be a multiple of the SF granularity (%u)", op->k, op->gran_k);
+    if (op->ld < op->k) return fail(DG_ERR_SHAPE, "%s: ld (%u) smaller than k (%u)", name, op->ld, op->k);
+    const uint32_t row_bytes = op->bits == 4 ? op->ld / 2 : op->ld;
+    if (row_bytes % 16 != 0) return fail(DG_ERR_SHAPE, "%s: row pitch %u bytes must be a multiple of 16", name, row_bytes);
+    const size_t storage = static_cast<size_t>(total_rows) * row_bytes;
+    if (op->data_len < storage) return fail(DG_ERR_SHAPE, "data buffer too small: %zu < %zu", op->data_len, storage);
+    const size_t sf_need = dg_sf_words(total_rows, op->k, op->gran_k, groups);
+    if (op->sf_len < sf_need) return fail(DG_ERR_SHAPE, "sf buffer too small: %zu < %zu", op->sf_len, sf_need);
+    return DG_OK;
+}
+
+struct Problem {
+    uint32_t type;
+    uint32_t m;            // rows per group (contiguous: whole arena)
+    uint32_t n, k, groups;
+    uint32_t expected_m;
+    const uint32_t* layout;
+};
+
+template <bool kMXF4, uint32_t kOut>
+cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
+    auto kernel = dg::dg_gemm_kernel<kMXF4, kOut>;
+    // the opt-in is per device; remember which devices already have it
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 64 || !(configured.load() & (1ull << dev))) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemCapacity));
+        if (e != cudaSuccess) return e;
+        if (dev < 64) configured.fetch_or(1ull << dev);
+    }
+    kernel<<<grid, dg::kNumThreads, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4]);
+    return cudaGetLastError();
+}
+
+int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi, const Problem& pr) {
+    if (out == nullptr || out->buf == nullptr) return fail(DG_ERR_SHAPE, "null output");
+    if (out->kind < DG_OUT_BF16 || out->kind > DG_OUT_FP8) return fail(DG_ERR_SHAPE, "invalid output kind %d", out->kind);
+    dg_epilogue e = {1.0f, 0, 0, 100};
+    if (epi) e = *epi;
+    if (out->kind == DG_OUT_FP8 && (e.has_alpha || e.accumulate))
+        return fail(DG_ERR_SHAPE, "the FP8-quantized output cannot combine alpha/accumulation");
+    if (e.accumulate && e.has_alpha) return fail(DG_ERR_SHAPE, "alpha and accumulation are mutually exclusive");
+    if (e.accumulate) return fail(DG_ERR_UNSUPPORTED, "accumulation into the output is not built yet");
+    if (a->k != b->k) return fail(DG_ERR_SHAPE, "a.k (%u) != b.k (%u)", a->k, b->k);
+    if (a->bits != b->bits) return fail(DG_ERR_UNSUPPORTED, "mixed FP8 x FP4 operands are not built yet");
+    if (pr.m == 0 || pr.n == 0) return DG_OK;
+    const bool contiguous = pr.type == DG_GEMM_M_GROUPED_CONTIGUOUS;
+    const uint32_t a_groups = contiguous || pr.type == DG_GEMM_NORMAL ? 1 : pr.groups;
+    const uint32_t b_groups = pr.type == DG_GEMM_NORMAL ? 1 : pr.groups;
+    int rc = check_operand(a, "a", pr.m * a_groups, a_groups);
+    if (rc) return rc;
+    rc = check_operand(b, "b", pr.n * b_groups, b_groups);
+    if (rc) return rc;
+    const uint32_t d_rows = pr.m * a_groups;
+    const uint32_t d_elem = out->kind == DG_OUT_F32 ? 4 : (out->kind == DG_OUT_FP8 ? 1 : 2);
+    if (out->ld < pr.n) return fail(DG_ERR_SHAPE, "output ld (%u) smaller than n (%u)", out->ld, pr.n);
+    if ((static_cast<size_t>(out->ld) * d_elem) % 16 != 0) return fail(DG_ERR_SHAPE, "output row pitch must be a multiple of 16 bytes");
+    if (out->buf_len < static_cast<size_t>(d_rows - 1) * out->ld + pr.n) return fail(DG_ERR_SHAPE, "output buffer too small");
+    if (out->kind == DG_OUT_FP8) {
+        if (out->sfd == nullptr) return fail(DG_ERR_SHAPE, "FP8 output needs sfd");
+        if (pr.n % 128 != 0) return fail(DG_ERR_SHAPE, "FP8 output needs n to be a multiple of 128");
+        if (out->sfd_len < static_cast<size_t>(pr.n / 128) * a_groups * align4(pr.m)) return fail(DG_ERR_SHAPE, "sfd buffer too small");
+    }
+    const uint32_t align = g_mk_alignment.load();
+    if (contiguous && align % 128 != 0)
+        return fail(DG_ERR_UNSUPPORTED, "contiguous layout: mk alignment %u is not a multiple of the 128-row tile", align);
+
+    dg_desc desc = {pr.type, pr.m, pr.n, pr.k, pr.groups, pr.expected_m, a->bits, b->bits, a->gran_k, b->gran_k,
+                    static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms)};
+    dg_config cfg;
+    rc = dg_best_config(&desc, &cfg);
+    if (rc) return rc;
+    static const bool print_cfg = [] { const char* v = getenv("DG_PRINT_CONFIGS"); return v && strcmp(v, "0") != 0; }();
+    if (print_cfg)
+        fprintf(stderr, "[dgb200] type=%u m=%u n=%u k=%u groups=%u -> block=128x%ux%u stages=%u accum=%u smem=%u tiles~%u\n", pr.type, pr.m, pr.n,
+                pr.k, pr.groups, cfg.block_n, cfg.block_k, cfg.num_stages, cfg.num_accum_stages, cfg.smem_size, cfg.num_tiles);
+
+    const bool mxf4 = a->bits == 4;
+    const uint32_t block_k = cfg.block_k;
+    const uint32_t sfa_words = 4 * a->gran_k >= block_k ? 1 : block_k / (4 * a->gran_k);
+    const uint32_t sfb_words = 4 * b->gran_k >= block_k ? 1 : block_k / (4 * b->gran_k);
+    const uint32_t sf_block_n = ceil_div(cfg.block_n, 128) * 128;
+
+    CUtensorMap maps[5];
+    {
+        const CUtensorMapDataType dt = mxf4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+        const uint64_t a_pitch = mxf4 ? a->ld / 2 : a->ld, b_pitch = mxf4 ? b->ld / 2 : b->ld;
+        uint64_t dims[3] = {pr.k, pr.m, a_groups};
+        uint64_t strides[2] = {a_pitch, a_pitch * pr.m};
+        uint32_t box[3] = {block_k, dg::kBlockM, 1};
+        rc = encode_map(&maps[0], dt, 3, a->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
+        if (rc) return rc;
+        uint64_t bdims[3] = {pr.k, pr.n, b_groups};
+        uint64_t bstrides[2] = {b_pitch, b_pitch * pr.n};
+        uint32_t bbox[3] = {block_k, cfg.block_n, 1};
+        rc = encode_map(&maps[1], dt, 3, b->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
+        if (rc) return rc;
+    }
+    const uint32_t sfa_cols = dg_sf_packed_cols(pr.k, a->gran_k), sfb_cols = dg_sf_packed_cols(pr.k, b->gran_k);
+    {
+        uint64_t dims[2] = {align4(pr.m), static_cast<uint64_t>(sfa_cols) * a_groups};
+        uint64_t strides[1] = {static_cast<uint64_t>(align4(pr.m)) * 4};
+        uint32_t box[2] = {128, sfa_words};
+        rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->sf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA");
+        if (rc) return rc;
+        uint64_t bdims[2] = {align4(pr.n), static_cast<uint64_t>(sfb_cols) * b_groups};
+        uint64_t bstrides[1] = {static_cast<uint64_t>(align4(pr.n)) * 4};
+        uint32_t bbox[2] = {sf_block_n, sfb_words};
+        rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, b->sf, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB");
+        if (rc) return rc;
+    }
+    {
+        const CUtensorMapDataType dt = out->kind == DG_OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : (out->kind == DG_OUT_FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+        const uint64_t pitch = static_cast<uint64_t>(out->ld) * d_elem;
+        uint64_t dims[3] = {pr.n, pr.m, a_groups};
+        uint64_t strides[2] = {pitch, pitch * pr.m};
+        uint32_t box[3] = {128 / d_elem, 32, 1};
+        rc = encode_map(&maps[4], dt, 3, out->buf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "D");
+        if (rc) return rc;
+    }
+
+    dg::GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.m = pr.m;
+    p.n = pr.n;
+    p.k = pr.k;
+    p.num_groups = pr.groups;
+    p.gemm_type = pr.type;
+    p.block_n = cfg.block_n;
+    p.num_stages = cfg.num_stages;
+    p.num_accum_stages = cfg.num_accum_stages;
+    p.gran_a = a->gran_k;
+    p.gran_b = b->gran_k;
+    p.sf_a_cols = sfa_cols;
+    p.sf_b_cols = sfb_cols;
+    p.mk_alignment = align;
+    p.has_alpha = e.has_alpha ? 1 : 0;
+    p.alpha = e.alpha;
+    p.sfd = out->sfd;
+    p.sfd_stride = align4(pr.m);
+    p.grouped_layout = pr.layout;
+    p.status = ctx->status;
+
+    uint32_t grid = static_cast<uint32_t>(ctx->num_sms);
+    if (pr.type == DG_GEMM_NORMAL || pr.type == DG_GEMM_BATCHED) grid = cfg.num_tiles < grid ? cfg.num_tiles : grid;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    cudaError_t ce;
+    if (mxf4) {
+        if (out->kind == DG_OUT_BF16) ce = launch_kernel<true, dg::kOutBf16>(p, grid, cfg.smem_size, ctx->stream, maps);
+        else if (out->kind == DG_OUT_F32) ce = launch_kernel<true, dg::kOutF32>(p, grid, cfg.smem_size, ctx->stream, maps);
+        else ce = launch_kernel<true, dg::kOutFp8>(p, grid, cfg.smem_size, ctx->stream, maps);
+    } else {
+        if (out->kind == DG_OUT_BF16) ce = launch_kernel<false, dg::kOutBf16>(p, grid, cfg.smem_size, ctx->stream, maps);
+        else if (out->kind == DG_OUT_F32) ce = launch_kernel<false, dg::kOutF32>(p, grid, cfg.smem_size, ctx->stream, maps);
+        else ce = launch_kernel<false, dg::kOutFp8>(p, grid, cfg.smem_size, ctx->stream, maps);
+    }
+    if (ce != cudaSuccess) return fail(DG_ERR_DRIVER, "kernel launch failed: %s", cudaGetErrorString(ce));
+    return DG_OK;
+}
+
+int ensure_group_ends(dg_ctx* ctx, uint32_t groups) {
+    if (ctx->group_ends_cap >= groups) return DG_OK;
+    if (ctx->group_ends) { cudaFree(ctx->group_ends); ctx->group_ends = nullptr; ctx->group_ends_cap = 0; }
+    const uint32_t cap = groups < 1024 ? 1024 : groups;
+    DG_CUDA(cudaMalloc(&ctx->group_ends, static_cast<size_t>(cap) * 4));
+    ctx->group_ends_cap = cap;
+    return DG_OK;
+}
+
+int run_group_ends(dg_ctx* ctx, const int32_t* m_indices, uint32_t m, uint32_t groups, uint32_t* ends) {
+    DG_CUDA(cudaMemsetAsync(ends, 0, static_cast<size_t>(groups) * 4, ctx->stream));
+    if (m > 0) dg::dg_group_ends_kernel<<<ceil_div(m, 256), 256, 0, ctx->stream>>>(m_indices, ends, groups, m);
+    dg::dg_group_ends_scan_kernel<<<1, 1024, 0, ctx->stream>>>(ends, groups);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dg_fp8_fp4_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi) {
+    if (!ctx || !a || !b || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (out->kind == DG_OUT_FP8) return fail(DG_ERR_SHAPE, "the dynamic FP8 output is only supported by the batched and masked APIs");
+    Problem pr = {DG_GEMM_NORMAL, a->rows, b->rows, a->k, 1, a->rows, nullptr};
+    return launch_gemm(ctx, a, b, out, epi, pr);
+}
+
+int dg_m_grouped_fp8_fp4_gemm_contiguous_ends(dg_ctx* ctx, const dg_lp_operand* a, const uint32_t* group_ends, const dg_lp_operand* b,
+                                              const dg_out* out, uint32_t num_groups, const dg_epilogue* epi) {
+    if (!ctx || !a || !b || !out || !group_ends) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_groups == 0 || b->rows % num_groups != 0) return fail(DG_ERR_SHAPE, "b.rows (%u) must be num_groups (%u) x n", b->rows, num_groups);
+    if (out->kind == DG_OUT_FP8) return fail(DG_ERR_SHAPE, "the dynamic FP8 output is only supported by the batched and masked APIs");
+    if (epi && epi->accumulate) return fail(DG_ERR_SHAPE, "accumulation is not supported by the grouped contiguous layout");
+    Problem pr = {DG_GEMM_M_GROUPED_CONTIGUOUS, a->rows, b->rows / num_groups, a->k, num_groups, a->rows, group_ends};
+    return launch_gemm(ctx, a, b, out, epi, pr);
+}
+
+int dg_m_grouped_fp8_fp4_gemm_contiguous(dg_ctx* ctx, const dg_lp_operand* a, const int32_t* m_indices, const dg_lp_operand* b,
+                                         const dg_out* out, uint32_t num_groups, const dg_epilogue* epi) {
+    if (!ctx || !a || !b || !out || !m_indices) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_groups == 0) return fail(DG_ERR_SHAPE, "num_groups must be positive");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    int rc = ensure_group_ends(ctx, num_groups);
+    if (rc) return rc;
+    rc = run_group_ends(ctx, m_indices, a->rows, num_groups, ctx->group_ends);
+    if (rc) return rc;
+    return dg_m_grouped_fp8_fp4_gemm_contiguous_ends(ctx, a, ctx->group_ends, b, out, num_groups, epi);
+}
+
+int dg_m_grouped_fp8_fp4_gemm_masked(dg_ctx* ctx, const dg_lp_operand* a, const int32_t* masked_m, const dg_lp_operand* b,
+                                     const dg_out* out, uint32_t num_groups, uint32_t expected_m, const dg_epilogue* epi) {
+    if (!ctx || !a || !b || !out || !masked_m) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_groups == 0 || b->rows % num_groups != 0) return fail(DG_ERR_SHAPE, "b.rows (%u) must be num_groups (%u) x n", b->rows, num_groups);
+    Problem pr = {DG_GEMM_M_GROUPED_MASKED, a->rows, b->rows / num_groups, a->k, num_groups, expected_m ? expected_m : 1,
+                  reinterpret_cast<const uint32_t*>(masked_m)};
+    return launch_gemm(ctx, a, b, out, epi, pr);
+}
+
+int dg_fp8_fp4_bmm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, uint32_t num_groups,
+                   const dg_epilogue* epi) {
+    if (!ctx || !a || !b || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_groups == 0) return fail(DG_ERR_SHAPE, "num_groups must be positive");
+    Problem pr = {DG_GEMM_BATCHED, a->rows, b->rows, a->k, num_groups, a->rows, nullptr};
+    return launch_gemm(ctx, a, b, out, epi, pr);
+}
+
+// ------------------------------------------------------------------ quantise / re-layout
+static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran, uint32_t groups, int rule,
+                       bool fp4, uint8_t* dst, uint32_t* sf) {
+    if (!ctx || !src || !dst || !sf) return fail(DG_ERR_SHAPE, "null argument");
+    if (groups == 0) groups = 1;
+    if (rows % groups != 0) return fail(DG_ERR_SHAPE, "rows (%u) must be a multiple of num_groups (%u)", rows, groups);
+    if (src_ld < k || src_ld % 8 != 0) return fail(DG_ERR_SHAPE, "src_ld (%u) must be >= k and a multiple of 8 elements", src_ld);
+    if (reinterpret_cast<uintptr_t>(src) % 16 != 0 || reinterpret_cast<uintptr_t>(dst) % 16 != 0)
+        return fail(DG_ERR_SHAPE, "src and dst must be 16-byte aligned");
+    if (rows == 0) return DG_OK;
+    dg::CastParams p;
+    p.src = src; p.dst = dst; p.sf = sf;
+    p.src_ld = src_ld; p.rows = rows; p.k = k; p.group_rows = rows / groups;
+    p.sf_cols = dg_sf_packed_cols(k, gran);
+    p.sf_stride = align4(rows / groups);
+    p.rule = rule;
+    const uint64_t units = static_cast<uint64_t>(rows) * ceil_div(k, 512);
+    const uint32_t blocks = static_cast<uint32_t>((units + 7) / 8);
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    if (fp4) dg::dg_cast_kernel<32, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    else if (gran == 32) dg::dg_cast_kernel<32, false><<<blocks, 256, 0, ctx->stream>>>(p);
+    else dg::dg_cast_kernel<128, false><<<blocks, 256, 0, ctx->stream>>>(p);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_cast_bf16_to_fp8_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran_k,
+                           uint32_t num_groups, uint8_t* dst, uint32_t* sf) {
+    if (gran_k != 32 && gran_k != 128) return fail(DG_ERR_SHAPE, "gran_k must be 32 or 128");
+    if (k == 0 || k % (gran_k * 4) != 0) return fail(DG_ERR_SHAPE, "k must be a multiple of %u for gran %u", gran_k * 4, gran_k);
+    return cast_common(ctx, src, src_ld, rows, k, gran_k, num_groups, 0, false, dst, sf);
+}
+
+int dg_cast_bf16_to_fp4_packed_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
+                                  int sf_rule, uint8_t* dst, uint32_t* sf) {
+    if (k == 0 || k % 128 != 0) return fail(DG_ERR_SHAPE, "fp4 k must be a multiple of 128");
+    if (sf_rule != DG_SF_RULE_REFERENCE_CPU && sf_rule != DG_SF_RULE_RANGE_FIT) return fail(DG_ERR_SHAPE, "unknown sf_rule %d", sf_rule);
+    return cast_common(ctx, src, src_ld, rows, k, 32, num_groups, sf_rule, true, dst, sf);
+}
+
+int dg_transform_sf(dg_ctx* ctx, const float* sf, uint32_t mn, uint32_t sf_k, uint32_t num_batches, float* dst) {
+    if (!ctx || !sf || !dst) return fail(DG_ERR_SHAPE, "null argument");
+    if (mn == 0 || sf_k == 0 || num_batches == 0) return DG_OK;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dim3 grid(ceil_div(align4(mn), 32), ceil_div(sf_k, 32), num_batches);
+    dg::dg_transpose_sf_kernel<<<grid, 256, 0, ctx->stream>>>(sf, dst, mn, sf_k, align4(mn));
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+static int sf_pack_common(dg_ctx* ctx, const float* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran, uint32_t groups,
+                          uint32_t mode, uint32_t* dst) {
+    if (!ctx || !src || !dst) return fail(DG_ERR_SHAPE, "null argument");
+    if (gran != 32 && gran != 128) return fail(DG_ERR_SHAPE, "gran_k must be 32 or 128");
+    if (groups == 0) groups = 1;
+    if (rows % groups != 0) return fail(DG_ERR_SHAPE, "rows (%u) must be a multiple of num_groups (%u)", rows, groups);
+    if (rows == 0 || k == 0) return DG_OK;
+    dg::SfPackParams p;
+    p.src = src; p.dst = dst; p.src_ld = src_ld; p.rows = rows; p.group_rows = rows / groups;
+    p.k_blocks = ceil_div(k, gran);
+    p.cols = ceil_div(p.k_blocks, 4);
+    p.dst_stride = align4(rows / groups);
+    p.mode = mode;
+    const uint64_t total = static_cast<uint64_t>(rows) * p.cols;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_sf_pack_kernel<<<static_cast<uint32_t>((total + 255) / 256), 256, 0, ctx->stream>>>(p);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_transform_sf1d_packed_ue8m0(dg_ctx* ctx, const float* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran_k,
+                                   uint32_t num_groups, uint32_t* dst) {
+    return sf_pack_common(ctx, src, src_ld, rows, k, gran_k, num_groups, 0, dst);
+}
+int dg_transform_sf2d_packed_ue8m0(dg_ctx* ctx, const float* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
+                                   uint32_t* dst) {
+    const uint32_t g = num_groups ? num_groups : 1;
+    if (g > 1 && (rows / g) % 128 != 0) return fail(DG_ERR_SHAPE, "2-D SF groups must own whole 128-row tiles (group rows %u)", rows / g);
+    return sf_pack_common(ctx, src, src_ld, rows, k, 128, num_groups, 1, dst);
+}
+int dg_transform_sf_t_packed_ue8m0(dg_ctx* ctx, const float* src, uint32_t rows, uint32_t k, uint32_t gran_k, uint32_t num_groups,
+                                   uint32_t* dst) {
+    const uint32_t g = num_groups ? num_groups : 1;
+    return sf_pack_common(ctx, src, align4(rows / g), rows, k, gran_k, num_groups, 2, dst);
+}
+
+int dg_group_ends_from_m_indices(dg_ctx* ctx, const int32_t* m_indices, uint32_t m, uint32_t num_groups, uint32_t* group_ends) {
+    if (!ctx || !m_indices || !group_ends) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_groups == 0) return DG_OK;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    return run_group_ends(ctx, m_indices, m, num_groups, group_ends);
+}
+
+int dg_unpack_fp4_raw(dg_ctx* ctx, const uint8_t* src, size_t packed_len, uint8_t* dst) {
+    if (!ctx || !src || !dst) return fail(DG_ERR_SHAPE, "null argument");
+    if (packed_len == 0) return DG_OK;
+    if (reinterpret_cast<uintptr_t>(src) % 16 != 0 || reinterpret_cast<uintptr_t>(dst) % 16 != 0)
+        return fail(DG_ERR_SHAPE, "src and dst must be 16-byte aligned");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    const uint64_t threads = (packed_len + 15) / 16;
+    dg::dg_unpack_fp4_kernel<<<static_cast<uint32_t>((threads + 255) / 256), 256, 0, ctx->stream>>>(src, dst, packed_len);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+}  // extern "C"

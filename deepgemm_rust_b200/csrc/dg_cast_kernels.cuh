@@ -1,0 +1,242 @@
+// Memory-bound kernels either side of the GEMM: bf16 -> e4m3 / e2m1 quantisation with packed
+// UE8M0 scale factors, f32 scale-factor re-layouts, and the group-end table of the contiguous
+// MoE layout.  All of them are HBM-bound byte/integer work: 16-byte loads and stores, one warp
+// per 512-element row segment, scale words written straight into the packed layout
+//   word(group g, local row r, column c) = sf[(g * cols + c) * align4(group_rows) + r],
+//   byte j of a word = exponent of K block 4c + j.
+#pragma once
+#include "dg_ptx.cuh"
+
+namespace dg {
+
+DG_DEVICE float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+DG_DEVICE float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// Biased exponent of amax, plus one if its mantissa exceeds the largest mantissa of the
+// target format (qmant = 0x600000 for 448, 0x400000 for 6).
+DG_DEVICE uint32_t rounded_exp(float amax, uint32_t qmant) { return (__float_as_uint(amax) + 0x7FFFFFu - qmant) >> 23; }
+
+DG_DEVICE uint32_t sf_exp_e4m3(float amax) {
+    const uint32_t r = rounded_exp(amax, 0x600000u);
+    const uint32_t e = (r < 8u ? 8u : r) - 8u;
+    return e < 105u ? 105u : e;
+}
+// rule 0: the reference crate's CPU MXFP4 rule max(rounded, 128); rule 1: smallest power of two
+// that brings the block maximum to 6 or below.
+DG_DEVICE uint32_t sf_exp_e2m1(float amax, int rule) {
+    const uint32_t r = rounded_exp(amax, 0x400000u);
+    if (rule == 0) { const uint32_t e = r < 128u ? 128u : r; return e > 255u ? 255u : e; }
+    const uint32_t e = (r < 2u ? 2u : r) - 2u;
+    return e < 1u ? 1u : e;
+}
+
+struct CastParams {
+    const uint16_t* src;   // (rows, src_ld) bf16
+    uint8_t* dst;          // (rows, k) e4m3 or (rows, k/2) packed e2m1
+    uint32_t* sf;          // packed scale words
+    uint32_t src_ld, rows, k, group_rows, sf_cols, sf_stride;
+    int rule;
+};
+
+// One warp quantises 512 consecutive K elements of one row: two 16-byte loads per lane
+// (elements [8*lane, +8) and [256 + 8*lane, +8)).  kGran = 128: 16 lanes share a scale, the
+// warp produces one scale word.  kGran = 32: 4 lanes share a scale, the warp produces 4 words.
+template <uint32_t kGran, bool kFp4>
+__global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
+    const uint32_t lane = threadIdx.x % 32;
+    const uint32_t segs_per_row = (p.k + 511) / 512;
+    const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    if (unit >= static_cast<uint64_t>(p.rows) * segs_per_row) return;
+    const uint32_t row = static_cast<uint32_t>(unit / segs_per_row), seg = static_cast<uint32_t>(unit % segs_per_row);
+    const uint32_t group = row / p.group_rows, local_row = row - group * p.group_rows;
+    const uint16_t* src_row = p.src + static_cast<size_t>(row) * p.src_ld;
+
+    uint4 raw[2];
+    uint32_t k0[2];
+    #pragma unroll
+    for (uint32_t h = 0; h < 2; ++h) {
+        k0[h] = seg * 512 + h * 256 + lane * 8;
+        raw[h] = k0[h] < p.k ? __ldg(reinterpret_cast<const uint4*>(src_row + k0[h])) : make_uint4(0, 0, 0, 0);
+    }
+    uint32_t exps[2];
+    #pragma unroll
+    for (uint32_t h = 0; h < 2; ++h) {
+        float v[8] = {bf16_lo(raw[h].x), bf16_hi(raw[h].x), bf16_lo(raw[h].y), bf16_hi(raw[h].y),
+                      bf16_lo(raw[h].z), bf16_hi(raw[h].z), bf16_lo(raw[h].w), bf16_hi(raw[h].w)};
+        float amax = 0.0f;
+        #pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        #pragma unroll
+        for (uint32_t d = kGran / 16; d >= 1; d /= 2) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
+        uint32_t e;
+        float inv;
+        if constexpr (kFp4) {
+            e = sf_exp_e2m1(amax, p.rule);
+            inv = p.rule == 0 ? 1.0f / __uint_as_float(e << 23) : __uint_as_float((254u - e) << 23);
+        } else {
+            e = sf_exp_e4m3(amax);
+            inv = __uint_as_float((254u - e) << 23);
+        }
+        exps[h] = e;
+        if (k0[h] < p.k) {
+            if constexpr (kFp4) {
+                float s[8];
+                #pragma unroll
+                for (uint32_t i = 0; i < 8; ++i) s[i] = v[i] * inv;
+                *reinterpret_cast<uint32_t*>(p.dst + static_cast<size_t>(row) * (p.k / 2) + k0[h] / 2) = cvt_e2m1x8(s);
+            } else {
+                // "+ 0.0f" turns an exact -0.0 product into +0.0: the oracle's encoder takes the
+                // sign from (v < 0), the hardware conversion would keep the sign bit
+                uint2 out;
+                out.x = cvt_e4m3x4(v[0] * inv + 0.0f, v[1] * inv + 0.0f, v[2] * inv + 0.0f, v[3] * inv + 0.0f);
+                out.y = cvt_e4m3x4(v[4] * inv + 0.0f, v[5] * inv + 0.0f, v[6] * inv + 0.0f, v[7] * inv + 0.0f);
+                *reinterpret_cast<uint2*>(p.dst + static_cast<size_t>(row) * p.k + k0[h]) = out;
+            }
+        }
+    }
+    // assemble scale words: exps[h] on lane l belongs to K block (seg*512 + h*256 + l*8) / kGran
+    if constexpr (kGran == 128) {
+        const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, exps[0], 0), e1 = __shfl_sync(0xFFFFFFFFu, exps[0], 16);
+        const uint32_t e2 = __shfl_sync(0xFFFFFFFFu, exps[1], 0), e3 = __shfl_sync(0xFFFFFFFFu, exps[1], 16);
+        if (lane == 0) {
+            const uint32_t blocks = (p.k + 127) / 128, b0 = seg * 4;
+            uint32_t w = e0;
+            if (b0 + 1 < blocks) w |= e1 << 8;
+            if (b0 + 2 < blocks) w |= e2 << 16;
+            if (b0 + 3 < blocks) w |= e3 << 24;
+            p.sf[(static_cast<size_t>(group) * p.sf_cols + seg) * p.sf_stride + local_row] = w;
+        }
+    } else {
+        // word c of this segment (c = 0..3) covers elements [c*128, +128): lanes 16*(c%2).. of half c/2
+        #pragma unroll
+        for (uint32_t c = 0; c < 4; ++c) {
+            const uint32_t h = c / 2, base = (c % 2) * 16;
+            const uint32_t src_exp = h == 0 ? exps[0] : exps[1];
+            const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, src_exp, base), b1 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 4);
+            const uint32_t b2 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 8), b3 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 12);
+            const uint32_t col = seg * 4 + c;
+            if (lane == c && col * 128 < p.k) {
+                const uint32_t blocks = (p.k + 31) / 32, first = col * 4;
+                uint32_t w = b0;
+                if (first + 1 < blocks) w |= b1 << 8;
+                if (first + 2 < blocks) w |= b2 << 16;
+                if (first + 3 < blocks) w |= b3 << 24;
+                p.sf[(static_cast<size_t>(group) * p.sf_cols + col) * p.sf_stride + local_row] = w;
+            }
+        }
+    }
+}
+
+// f32 power-of-two scales -> packed UE8M0 words (exponent byte, mantissa dropped, K tail = 127).
+//   mode 0: src (rows, src_ld) one scale per row per K block
+//   mode 1: src (ceil(rows/128), src_ld) one scale per 128x128 tile, expanded per row
+//   mode 2: src (groups * k_blocks, src_ld = align4(group_rows)) rows contiguous (transposed form)
+struct SfPackParams {
+    const float* src;
+    uint32_t* dst;
+    uint32_t src_ld, rows, group_rows, k_blocks, cols, dst_stride, mode;
+};
+__global__ void __launch_bounds__(256) dg_sf_pack_kernel(const SfPackParams p) {
+    // consecutive threads take consecutive rows of one word column: the writes coalesce
+    const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= static_cast<uint64_t>(p.rows) * p.cols) return;
+    const uint32_t col = static_cast<uint32_t>(idx / p.rows), row = static_cast<uint32_t>(idx % p.rows);
+    const uint32_t group = row / p.group_rows, local_row = row - group * p.group_rows;
+    uint32_t w = 0;
+    #pragma unroll
+    for (uint32_t j = 0; j < 4; ++j) {
+        const uint32_t kc = col * 4 + j;
+        uint32_t bits = 0x3F800000u;
+        if (kc < p.k_blocks) {
+            if (p.mode == 0) bits = __float_as_uint(__ldg(p.src + static_cast<size_t>(row) * p.src_ld + kc));
+            else if (p.mode == 1) bits = __float_as_uint(__ldg(p.src + static_cast<size_t>(row / 128) * p.src_ld + kc));
+            else bits = __float_as_uint(__ldg(p.src + (static_cast<size_t>(group) * p.k_blocks + kc) * p.src_ld + local_row));
+        }
+        w |= ((bits >> 23) & 0xFFu) << (8 * j);
+    }
+    p.dst[(static_cast<size_t>(group) * p.cols + col) * p.dst_stride + local_row] = w;
+}
+
+// (batches, mn, sf_k) f32 -> (batches * sf_k, align4(mn)) f32, padding columns zero.
+// 32x32 tiles through shared memory so both the reads and the writes coalesce.
+__global__ void __launch_bounds__(256) dg_transpose_sf_kernel(const float* __restrict__ src, float* __restrict__ dst, uint32_t mn,
+                                                              uint32_t sf_k, uint32_t aligned_mn) {
+    __shared__ float tile[32][33];
+    const uint32_t b = blockIdx.z, r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const uint32_t tx = threadIdx.x % 32, ty = threadIdx.x / 32;
+    for (uint32_t i = ty; i < 32; i += 8) {
+        const uint32_t r = r0 + i, c = c0 + tx;
+        tile[i][tx] = (r < mn && c < sf_k) ? src[(static_cast<size_t>(b) * mn + r) * sf_k + c] : 0.0f;
+    }
+    __syncthreads();
+    for (uint32_t i = ty; i < 32; i += 8) {
+        const uint32_t c = c0 + i, r = r0 + tx;
+        if (c < sf_k && r < aligned_mn) dst[(static_cast<size_t>(b) * sf_k + c) * aligned_mn + r] = tile[tx][i];
+    }
+}
+
+// Group-end table of the contiguous layout: ends[g] = 1 + last row whose m_indices == g.
+// Step 1 (grid): atomicMax per row.  Step 2 (one block): running maximum, so a group without
+// rows inherits the previous end and the scheduler's prefix walk stays monotone.
+__global__ void __launch_bounds__(256) dg_group_ends_kernel(const int32_t* __restrict__ m_indices, uint32_t* ends, uint32_t groups,
+                                                            uint32_t m) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= m) return;
+    const int32_t g = __ldg(m_indices + i);
+    if (g < 0 || static_cast<uint32_t>(g) >= groups) return;
+    // only the last row of a run needs to publish
+    if (i + 1 < m && __ldg(m_indices + i + 1) == g) return;
+    atomicMax(ends + g, static_cast<uint32_t>(i) + 1);
+}
+__global__ void __launch_bounds__(1024) dg_group_ends_scan_kernel(uint32_t* ends, uint32_t groups) {
+    // inclusive running maximum over `groups` entries, 1024 threads, any length
+    __shared__ uint32_t warp_max[32];
+    __shared__ uint32_t carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < groups; base += 1024) {
+        const uint32_t i = base + threadIdx.x;
+        uint32_t v = i < groups ? ends[i] : 0u;
+        #pragma unroll
+        for (uint32_t d = 1; d < 32; d *= 2) {
+            const uint32_t o = __shfl_up_sync(0xFFFFFFFFu, v, d);
+            if (threadIdx.x % 32 >= d) v = max(v, o);
+        }
+        if (threadIdx.x % 32 == 31) warp_max[threadIdx.x / 32] = v;
+        __syncthreads();
+        uint32_t prefix = carry;
+        for (uint32_t w = 0; w < threadIdx.x / 32; ++w) prefix = max(prefix, warp_max[w]);
+        v = max(v, prefix);
+        if (i < groups) ends[i] = v;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = v;
+        __syncthreads();
+    }
+}
+
+// Packed e2m1 -> one code per byte (low nibble), 16 bytes in, 32 bytes out per thread.
+__global__ void __launch_bounds__(256) dg_unpack_fp4_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t packed_len) {
+    const uint64_t i = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 16;
+    if (i + 16 <= packed_len) {
+        const uint4 v = *reinterpret_cast<const uint4*>(src + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[8];
+        #pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) {
+            // byte b of w -> two output bytes (low nibble, high nibble)
+            const uint32_t lo = w[q] & 0x0F0F0F0Fu, hi = (w[q] >> 4) & 0x0F0F0F0Fu;
+            o[2 * q] = __byte_perm(lo, hi, 0x5140);
+            o[2 * q + 1] = __byte_perm(lo, hi, 0x7362);
+        }
+        uint4* out = reinterpret_cast<uint4*>(dst + 2 * i);
+        out[0] = make_uint4(o[0], o[1], o[2], o[3]);
+        out[1] = make_uint4(o[4], o[5], o[6], o[7]);
+    } else {
+        for (uint64_t j = i; j < packed_len; ++j) {
+            dst[2 * j] = src[j] & 0x0F;
+            dst[2 * j + 1] = src[j] >> 4;
+        }
+    }
+}
+
+}  // namespace dg

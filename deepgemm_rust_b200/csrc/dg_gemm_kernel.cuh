@@ -1,0 +1,445 @@
+// Persistent, warp-specialised block-scaled GEMM for sm_100a.
+//
+//   D[g][m, n] = epilogue( sum_k (A[g][m, k] * 2^(sfa-127)) * (B[g][n, k] * 2^(sfb-127)) )
+//
+// A and B are K-major e4m3 bytes (kind::mxf8f6f4) or packed e2m1 nibbles (kind::mxf4); the
+// UE8M0 scale factors arrive as packed u32 words (rows contiguous, one word per 4 scale
+// blocks along K) and are applied by the tensor core itself (tcgen05.mma ... block_scale).
+//
+// Roles inside one 256-thread CTA (one CTA per SM, looping over output tiles):
+//   warp 0      lane 0 issues every TMA load: A/B tiles into a ring of 128B-swizzled stages,
+//               scale-factor words into the same stage's raw scale area
+//   warp 1      allocates TMEM; lane 0 copies scales smem->TMEM (tcgen05.cp) and issues the
+//               UMMAs; tcgen05.commit releases the stage and, after the last k-block,
+//               publishes the accumulator
+//   warp 2      re-orders each 128-word scale chunk from row order to the 32x4 order the
+//               tensor core reads (row r -> lane r%32, column r/32)
+//   warp 3      idle
+//   warps 4-7   epilogue: TMEM -> registers -> {bf16 | f32 | e4m3 + UE8M0 row scales}
+//               -> swizzled staging -> TMA store; each warp owns 32 rows and stores on its own
+// Accumulators are double-buffered in TMEM whenever 2*BLOCK_N plus the scale columns fit
+// in 512 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
+#pragma once
+#include "dg_ptx.cuh"
+
+namespace dg {
+
+enum GemmType : uint32_t { kGemmNormal = 0, kGemmContiguous = 1, kGemmMasked = 2, kGemmBatched = 3 };
+enum OutKind : uint32_t { kOutBf16 = 0, kOutF32 = 1, kOutFp8 = 2 };
+
+constexpr uint32_t kBlockM = 128;          // UMMA M, rows of A per tile
+constexpr uint32_t kBlockKBytes = 128;     // one 128-byte swizzle row of K per stage
+constexpr uint32_t kUmmaKBytes = 32;       // K bytes consumed by one UMMA
+constexpr uint32_t kMaxStages = 12;
+constexpr uint32_t kNumThreads = 256;
+constexpr uint32_t kEpilogueBufBytes = 4096;  // 32 rows x 128 bytes per warp per buffer
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmParams {
+    uint32_t m, n, k;          // m: rows per group (contiguous: rows of the whole arena)
+    uint32_t num_groups;
+    uint32_t gemm_type;
+    uint32_t block_n;
+    uint32_t num_stages;
+    uint32_t num_accum_stages;
+    uint32_t gran_a, gran_b;   // K elements per scale factor (32 or 128)
+    uint32_t sf_a_cols, sf_b_cols;  // packed words per row (per group) along K
+    uint32_t mk_alignment;     // contiguous layout: every group starts at a multiple of this
+    uint32_t has_alpha;
+    float alpha;
+    uint32_t sfd_stride;       // output scale words: stride between word columns (fp8 output)
+    const uint32_t* grouped_layout;  // contiguous: end row of each group; masked: valid rows per group
+    uint32_t* sfd;
+    Status* status;
+};
+
+struct Tile {
+    uint32_t m0, n0;     // first row / column of the tile (row is group-local except in the contiguous arena)
+    uint32_t ga, gb;     // group coordinate of A/D and of B
+};
+
+// Walks the tile list of one CTA.  Every role runs its own copy and sees the same sequence.
+struct Scheduler {
+    const GemmParams& p;
+    uint32_t num_m_blocks, num_n_blocks, iter;
+    uint32_t cur_group, cum_begin, cur_m_blocks, cur_row_start;
+
+    DG_DEVICE explicit Scheduler(const GemmParams& params) : p(params) {
+        num_m_blocks = (p.m + kBlockM - 1) / kBlockM;
+        num_n_blocks = (p.n + p.block_n - 1) / p.block_n;
+        iter = 0;
+        cur_group = 0;
+        cum_begin = 0;
+        cur_m_blocks = 0;
+        cur_row_start = 0;
+        if (p.gemm_type == kGemmContiguous || p.gemm_type == kGemmMasked) load_group();
+    }
+
+    DG_DEVICE void load_group() {
+        if (cur_group >= p.num_groups) return;
+        if (p.gemm_type == kGemmContiguous) {
+            const uint32_t prev_end = cur_group == 0 ? 0u : __ldg(p.grouped_layout + cur_group - 1);
+            const uint32_t end = __ldg(p.grouped_layout + cur_group);
+            cur_row_start = (prev_end + p.mk_alignment - 1) / p.mk_alignment * p.mk_alignment;
+            const uint32_t rows = end > cur_row_start ? end - cur_row_start : 0u;
+            cur_m_blocks = (rows + kBlockM - 1) / kBlockM;
+        } else {
+            const int32_t valid = static_cast<int32_t>(__ldg(p.grouped_layout + cur_group));
+            const uint32_t rows = valid <= 0 ? 0u : (static_cast<uint32_t>(valid) < p.m ? static_cast<uint32_t>(valid) : p.m);
+            cur_row_start = 0;
+            cur_m_blocks = (rows + kBlockM - 1) / kBlockM;
+        }
+    }
+
+    DG_DEVICE bool next(Tile& t) {
+        const uint32_t idx = blockIdx.x + (iter++) * gridDim.x;
+        if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmBatched) {
+            const uint32_t per_group = num_m_blocks * num_n_blocks;
+            if (idx >= per_group * p.num_groups) return false;
+            const uint32_t g = idx / per_group, r = idx - g * per_group;
+            // bands of 16 row-blocks, rows fastest inside a band: the tiles in flight at
+            // any moment form a compact patch, so A and B tiles are re-read from L2
+            constexpr uint32_t kBand = 16;
+            const uint32_t per_band = kBand * num_n_blocks;
+            const uint32_t band = r / per_band, in_band = r - band * per_band;
+            const uint32_t first_m = band * kBand;
+            const uint32_t rows_here = num_m_blocks - first_m < kBand ? num_m_blocks - first_m : kBand;
+            const uint32_t nb = in_band / rows_here, mb = first_m + (in_band - nb * rows_here);
+            t.m0 = mb * kBlockM;
+            t.n0 = nb * p.block_n;
+            t.ga = t.gb = g;
+            return true;
+        }
+        while (true) {
+            if (cur_group >= p.num_groups) return false;
+            const uint32_t end = cum_begin + cur_m_blocks * num_n_blocks;
+            if (idx < end) break;
+            cum_begin = end;
+            ++cur_group;
+            load_group();
+        }
+        const uint32_t in_group = idx - cum_begin;
+        const uint32_t nb = in_group / cur_m_blocks, ml = in_group - nb * cur_m_blocks;
+        t.m0 = cur_row_start + ml * kBlockM;
+        t.n0 = nb * p.block_n;
+        t.gb = cur_group;
+        t.ga = p.gemm_type == kGemmContiguous ? 0u : cur_group;
+        return true;
+    }
+};
+
+// How often a scale word must be (re)loaded and how many words one k-block needs.
+//   block_k_elems = 128 (e4m3) or 256 (e2m1 pairs).  A word covers 4*gran elements.
+struct SfPlan {
+    uint32_t period;  // load on k-blocks where kb % period == 0
+    uint32_t words;   // words per row per load
+};
+DG_DEVICE SfPlan sf_plan(uint32_t gran, uint32_t block_k_elems) {
+    const uint32_t per_word = 4 * gran;
+    SfPlan s;
+    if (per_word >= block_k_elems) { s.period = per_word / block_k_elems; s.words = 1; }
+    else { s.period = 1; s.words = block_k_elems / per_word; }
+    return s;
+}
+
+template <bool kMXF4, uint32_t kOut>
+__global__ void __launch_bounds__(kNumThreads, 1)
+dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+               const __grid_constant__ CUtensorMap tmap_d) {
+    constexpr uint32_t kBlockKElems = kMXF4 ? 256 : 128;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t block_n = p.block_n;
+    const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
+    const SfPlan plan_a = sf_plan(p.gran_a, kBlockKElems), plan_b = sf_plan(p.gran_b, kBlockKElems);
+    const uint32_t sfa_bytes = 512 * plan_a.words, sfb_bytes = sf_block_n * 4 * plan_b.words;
+    const uint32_t a_bytes = kBlockM * kBlockKBytes, b_bytes = block_n * kBlockKBytes;
+    const uint32_t num_stages = p.num_stages;
+    const uint32_t num_k_blocks = (p.k + kBlockKElems - 1) / kBlockKElems;
+
+    // shared memory carve-up (every tile base stays 1024-byte aligned)
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem_a + num_stages * a_bytes;
+    uint8_t* smem_epi = smem_b + num_stages * b_bytes;
+    uint8_t* smem_sfa = smem_epi + 8 * kEpilogueBufBytes;
+    uint8_t* smem_sfb = smem_sfa + num_stages * sfa_bytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sfb + num_stages * sfb_bytes);
+    uint64_t* bar_full = bars;
+    uint64_t* bar_empty = bars + kMaxStages;
+    uint64_t* bar_sf_raw = bars + 2 * kMaxStages;
+    uint64_t* bar_sf_ready = bars + 3 * kMaxStages;
+    uint64_t* bar_tmem_full = bars + 4 * kMaxStages;
+    uint64_t* bar_tmem_empty = bars + 4 * kMaxStages + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kMaxStages + 4);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < num_stages; ++s) {
+            mbar_init(bar_full + s, 1);
+            mbar_init(bar_empty + s, 1);
+            mbar_init(bar_sf_raw + s, 1);
+            mbar_init(bar_sf_ready + s, 1);
+        }
+        for (uint32_t e = 0; e < 2; ++e) {
+            mbar_init(bar_tmem_full + e, 1);
+            mbar_init(bar_tmem_empty + e, 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_sfa);
+        tma_prefetch_desc(&tmap_sfb);
+        tma_prefetch_desc(&tmap_d);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(tmem_slot, kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_sfa = tmem_base + p.num_accum_stages * block_n;
+    const uint32_t tmem_sfb = tmem_sfa + 4 * plan_a.words;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            Scheduler sched(p);
+            Tile t;
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            while (ok && sched.next(t)) {
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                    if (!mbar_wait(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
+                    const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                    if (need_a || need_b) {
+                        mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_bytes : 0u));
+                        if (need_a)
+                            tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, static_cast<int32_t>(t.m0),
+                                        static_cast<int32_t>(t.ga * p.sf_a_cols + kb / plan_a.period * plan_a.words));
+                        if (need_b)
+                            tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0),
+                                        static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words));
+                    }
+                    mbar_arrive_expect_tx(bar_full + stage, a_bytes + b_bytes);
+                    const int32_t kx = static_cast<int32_t>(kb * kBlockKElems);
+                    tma_load_3d(smem_a + stage * a_bytes, &tmap_a, bar_full + stage, kx, static_cast<int32_t>(t.m0),
+                                static_cast<int32_t>(t.ga));
+                    tma_load_3d(smem_b + stage * b_bytes, &tmap_b, bar_full + stage, kx, static_cast<int32_t>(t.n0),
+                                static_cast<int32_t>(t.gb));
+                    if (++stage == num_stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- UMMA issuer
+        if (lane == 0) {
+            Scheduler sched(p);
+            Tile t;
+            uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0;
+            const uint32_t idesc = make_idesc_block_scaled(kBlockM, block_n, kMXF4 ? 1u : 0u, kMXF4 ? 1u : 0u);
+            bool ok = true;
+            while (ok && sched.next(t)) {
+                const uint32_t e = it % p.num_accum_stages, acc_phase = (it / p.num_accum_stages) & 1;
+                ++it;
+                if (!mbar_wait(bar_tmem_empty + e, acc_phase ^ 1, abort_flag, p.status, 0x200 + e)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + e * block_n;
+                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                    const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                    if (!mbar_wait(bar_full + stage, phase, abort_flag, p.status, 0x300 + stage)) { ok = false; break; }
+                    if (need_a || need_b) {
+                        if (!mbar_wait(bar_sf_ready + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x400 + stage)) { ok = false; break; }
+                        sf_phase_bits ^= 1u << stage;
+                    }
+                    tc_fence_after();
+                    if (need_a) {
+                        for (uint32_t c = 0; c < plan_a.words; ++c)
+                            utccp_32x128b_warpx4<1>(tmem_sfa + 4 * c, make_smem_desc(smem_u32(smem_sfa + stage * sfa_bytes + c * 512), 0, 128, 0));
+                    }
+                    if (need_b) {
+                        for (uint32_t c = 0; c < plan_b.words * (sf_block_n / 128); ++c)
+                            utccp_32x128b_warpx4<1>(tmem_sfb + 4 * c, make_smem_desc(smem_u32(smem_sfb + stage * sfb_bytes + c * 512), 0, 128, 0));
+                    }
+                    const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes), 0, 1024, 2);
+                    const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes), 0, 1024, 2);
+                    #pragma unroll
+                    for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+                        uint32_t a_id, b_id, a_col, b_col;
+                        if constexpr (kMXF4) {
+                            // one UMMA spans 64 elements = two scale bytes; a word spans two UMMAs
+                            a_id = (k & 1) * 2; b_id = (k & 1) * 2;
+                            a_col = 4 * (k / 2); b_col = 4 * (k / 2) * (sf_block_n / 128);
+                        } else {
+                            a_id = p.gran_a == 128 ? kb % 4 : k;
+                            b_id = p.gran_b == 128 ? kb % 4 : k;
+                            a_col = 0; b_col = 0;
+                        }
+                        umma_block_scaled<1, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4),
+                                                    idesc_with_sf_ids(idesc, a_id, b_id), tmem_sfa + a_col, tmem_sfb + b_col,
+                                                    (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar_empty + stage);
+                    if (kb + 1 == num_k_blocks) umma_commit(bar_tmem_full + e);
+                    if (++stage == num_stages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 2) {
+        // -------------------------------------------------- scale-factor re-ordering
+        Scheduler sched(p);
+        Tile t;
+        uint32_t stage = 0, sf_phase_bits = 0;
+        bool ok = true;
+        while (ok && sched.next(t)) {
+            for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                if (need_a || need_b) {
+                    if (!mbar_wait(bar_sf_raw + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x500 + stage)) { ok = false; break; }
+                    sf_phase_bits ^= 1u << stage;
+                    // word r of a 128-word chunk moves to position (r % 32) * 4 + r / 32
+                    const uint32_t chunks_a = need_a ? plan_a.words : 0u;
+                    const uint32_t chunks_b = need_b ? plan_b.words * (sf_block_n / 128) : 0u;
+                    for (uint32_t c = 0; c < chunks_a + chunks_b; ++c) {
+                        uint32_t* chunk = reinterpret_cast<uint32_t*>(c < chunks_a ? smem_sfa + stage * sfa_bytes + c * 512
+                                                                                   : smem_sfb + stage * sfb_bytes + (c - chunks_a) * 512);
+                        const uint32_t w0 = chunk[lane], w1 = chunk[32 + lane], w2 = chunk[64 + lane], w3 = chunk[96 + lane];
+                        __syncwarp();
+                        st_shared_v4(smem_u32(chunk + lane * 4), w0, w1, w2, w3);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_sf_ready + stage);
+                }
+                if (++stage == num_stages) stage = 0;
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t ew = warp - 4;  // TMEM lane quadrant and 32-row slice of the tile
+        uint8_t* buf0 = smem_epi + ew * 2 * kEpilogueBufBytes;
+        constexpr uint32_t kSubsPerBuf = kOut == kOutBf16 ? 2 : (kOut == kOutF32 ? 1 : 4);  // 32-column steps per 128-byte row
+        constexpr uint32_t kColsPerBuf = 32 * kSubsPerBuf;
+        Scheduler sched(p);
+        Tile t;
+        uint32_t it = 0, buf_idx = 0;
+        while (sched.next(t)) {
+            const uint32_t e = it % p.num_accum_stages, acc_phase = (it / p.num_accum_stages) & 1;
+            ++it;
+            if (!mbar_wait(bar_tmem_full + e, acc_phase, abort_flag, p.status, 0x600 + e)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((ew * 32) << 16) + e * block_n;
+            const uint32_t row = t.m0 + ew * 32 + lane;  // row this thread owns
+            const uint32_t num_subs = block_n / 32;
+            uint32_t sf_word = 0;
+            for (uint32_t s = 0; s < num_subs; ++s) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(taddr + s * 32, v);
+                tmem_ld_wait_x32(v);
+                if (s + 1 == num_subs) {
+                    // the accumulator is in registers: hand the TMEM stage back to the UMMA warp
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tmem_empty + e);
+                }
+                const uint32_t sub_in_buf = s % kSubsPerBuf;
+                uint8_t* buf = buf0 + buf_idx * kEpilogueBufBytes;
+                if (sub_in_buf == 0) {
+                    // the store issued two buffers ago must have finished reading this buffer
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                }
+                if (p.has_alpha) {
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
+                }
+                const uint32_t row_addr = smem_u32(buf) + lane * 128;
+                if constexpr (kOut == kOutBf16) {
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint32_t chunk = (sub_in_buf * 4 + j) ^ (lane & 7);
+                        st_shared_v4(row_addr + chunk * 16,
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1])),
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5])),
+                                     pack_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7])));
+                    }
+                } else if constexpr (kOut == kOutF32) {
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        const uint32_t chunk = j ^ (lane & 7);
+                        st_shared_v4(row_addr + chunk * 16, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
+                } else {
+                    // round to bf16 first, take the block maximum on the bf16 bit patterns, pick the
+                    // power-of-two scale that brings it under 448, quantise the rounded values
+                    uint32_t amax = 0;
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 32; i += 2) {
+                        const uint32_t pk = pack_bf16x2(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                        v[i] = pk << 16;            // bf16 widened back to f32 bits
+                        v[i + 1] = pk & 0xFFFF0000u;
+                        amax = max(amax, max((pk & 0x7FFFu), ((pk >> 16) & 0x7FFFu)));
+                    }
+                    const uint32_t rounded = (amax + 0x7Fu - 0x60u) >> 7;
+                    uint32_t sf_exp = (rounded < 8u ? 8u : rounded) - 8u;
+                    sf_exp = sf_exp < 105u ? 105u : sf_exp;
+                    const float inv = __uint_as_float((254u - sf_exp) << 23);
+                    sf_word |= sf_exp << (8 * sub_in_buf);
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 2; ++j) {
+                        const uint32_t chunk = (sub_in_buf * 2 + j) ^ (lane & 7);
+                        uint32_t w[4];
+                        #pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q)
+                            w[q] = cvt_e4m3x4(__uint_as_float(v[16 * j + 4 * q + 0]) * inv + 0.0f, __uint_as_float(v[16 * j + 4 * q + 1]) * inv + 0.0f,
+                                              __uint_as_float(v[16 * j + 4 * q + 2]) * inv + 0.0f, __uint_as_float(v[16 * j + 4 * q + 3]) * inv + 0.0f);
+                        st_shared_v4(row_addr + chunk * 16, w[0], w[1], w[2], w[3]);
+                    }
+                }
+                if (sub_in_buf + 1 == kSubsPerBuf) {
+                    const uint32_t col0 = t.n0 + (s / kSubsPerBuf) * kColsPerBuf;
+                    if constexpr (kOut == kOutFp8) {
+                        if (row < p.m && col0 < p.n)
+                            p.sfd[static_cast<size_t>(t.ga * (p.n / 128) + col0 / 128) * p.sfd_stride + row] = sf_word;
+                        sf_word = 0;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (col0 < p.n && t.m0 + ew * 32 < p.m)
+                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(t.m0 + ew * 32), static_cast<int32_t>(t.ga));
+                        tma_store_commit();
+                    }
+                    buf_idx ^= 1;
+                }
+            }
+        }
+        if (lane == 0) tma_store_wait<0>();
+        __syncwarp();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc<1>(tmem_base, kTmemCols);
+    }
+}
+
+// Bytes of dynamic shared memory the kernel needs for a configuration (host side).
+inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t stages, uint32_t sfa_words, uint32_t sfb_words) {
+    const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
+    const uint32_t per_stage = kBlockM * kBlockKBytes + block_n * kBlockKBytes + 512 * sfa_words + sf_block_n * 4 * sfb_words;
+    return 1024 + stages * per_stage + 8 * kEpilogueBufBytes + (4 * kMaxStages + 4) * 8 + 16;
+}
+
+}  // namespace dg

@@ -1,0 +1,171 @@
+/*
+ * dgb200 -- C ABI of the B200 (sm_100a) block-scaled FP8/FP4 GEMM library.
+ *
+ * This is the boundary a host in another language binds to.  Each entry point
+ * names the interface of the reference crate (idrees2516/deepgemm-rust, paths
+ * relative to that crate) it stands in for.  All pointers named "device" are
+ * raw CUDA device addresses; nothing here takes or returns a framework type.
+ * Work is enqueued on the context's stream and the call returns without
+ * synchronising, like the reference.  Every function returns a dg_status;
+ * dg_last_error() gives the message of the calling thread's last failure.
+ *
+ * There is no CPU fallback: without a CUDA device dg_ctx_create fails.
+ */
+#ifndef DGB200_H_
+#define DGB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* deepgemm/src/types.rs:9-21 (DgError) plus a code for a device-side wait that ran out. */
+typedef enum {
+    DG_OK = 0,
+    DG_ERR_DRIVER = 1,
+    DG_ERR_SHAPE = 2,
+    DG_ERR_UNSUPPORTED = 3,
+    DG_ERR_TIMEOUT = 4
+} dg_status;
+
+typedef struct dg_ctx dg_ctx;
+
+/* deepgemm/src/device.rs:40-56 (DgContext::new): one device, one stream. */
+int dg_ctx_create(int ordinal, dg_ctx** out);
+/* Same, adopting a stream the caller owns (e.g. the current stream of a tensor library). */
+int dg_ctx_create_on_stream(int ordinal, void* cuda_stream, dg_ctx** out);
+int dg_ctx_destroy(dg_ctx* ctx);
+/* device.rs:129 (sync).  Also reports DG_ERR_TIMEOUT if a kernel gave up on a wait. */
+int dg_ctx_sync(dg_ctx* ctx);
+/* device.rs:124 (num_sms) */
+int dg_ctx_num_sms(const dg_ctx* ctx, int* out);
+void* dg_ctx_stream(const dg_ctx* ctx);
+int dg_ctx_set_stream(dg_ctx* ctx, void* cuda_stream);
+/* Reads the device status word without synchronising the stream first (the caller has). */
+int dg_ctx_check_status(dg_ctx* ctx);
+const char* dg_last_error(void);
+
+/* deepgemm/src/ops_sm100.rs:33-45 (LpOperand).  data: (rows, ld) K-major e4m3 bytes, or packed
+ * e2m1 with ld counted in logical elements; sf: packed UE8M0 words, see dg_sf_words. */
+typedef struct {
+    const void* data;     /* device */
+    const uint32_t* sf;   /* device */
+    uint32_t rows, k, ld;
+    uint32_t bits;        /* 8 = e4m3, 4 = packed e2m1 */
+    uint32_t gran_k;      /* 32 or 128 */
+    uint32_t major_mn;    /* must be 0: K-major operands only */
+    size_t data_len;      /* bytes available at data */
+    size_t sf_len;        /* words available at sf */
+} dg_lp_operand;
+
+/* ops_sm100.rs:95-110 (Sm100Out) */
+enum { DG_OUT_BF16 = 0, DG_OUT_F32 = 1, DG_OUT_FP8 = 2 };
+typedef struct {
+    int kind;
+    void* buf;            /* device; (rows, ld) elements of the kind */
+    uint32_t ld;
+    uint32_t* sfd;        /* device; DG_OUT_FP8 only: (ceil(n/128) [* groups], align4(m)) words */
+    size_t buf_len;       /* elements available at buf */
+    size_t sfd_len;       /* words available at sfd */
+} dg_out;
+
+/* ops_sm100.rs:114-131 (Sm100Epilogue) */
+typedef struct {
+    float alpha;
+    int has_alpha;
+    int accumulate;       /* not supported: DG_ERR_UNSUPPORTED */
+    uint32_t tc_util;     /* accepted, ignored (100 = unthrottled) */
+} dg_epilogue;
+
+/* ops_sm100.rs:719 (fp8_fp4_gemm_dev): D[m,n] = alpha * A[m,k] . B[n,k]^T */
+int dg_fp8_fp4_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi);
+
+/* ops_sm100.rs:759 (m_grouped_fp8_fp4_gemm_contiguous_dev).  a: (m_total, k) arena, every group
+ * starts at a multiple of the mk alignment; m_indices (device, m_total int32): group of each
+ * row, -1 for padding; b.rows = num_groups * n.  The group-end table is built in a scratch
+ * buffer the context owns. */
+int dg_m_grouped_fp8_fp4_gemm_contiguous(dg_ctx* ctx, const dg_lp_operand* a, const int32_t* m_indices, const dg_lp_operand* b,
+                                         const dg_out* out, uint32_t num_groups, const dg_epilogue* epi);
+/* Same with a caller-built group-end table (device, num_groups uint32, non-decreasing):
+ * group_ends[g] = one past the last row of group g (what dg_group_ends_from_m_indices writes). */
+int dg_m_grouped_fp8_fp4_gemm_contiguous_ends(dg_ctx* ctx, const dg_lp_operand* a, const uint32_t* group_ends, const dg_lp_operand* b,
+                                              const dg_out* out, uint32_t num_groups, const dg_epilogue* epi);
+
+/* ops_sm100.rs:815 (m_grouped_fp8_fp4_gemm_masked_dev).  a.rows = m_max (per group), data
+ * (num_groups, m_max, k); b.rows = num_groups * n; masked_m (device, int32 per group) is read on
+ * the device.  Unlike the reference, DG_OUT_FP8 is accepted here: D is (num_groups, m_max, n)
+ * e4m3 and sfd takes the grouped packed layout with gran 32 along n. */
+int dg_m_grouped_fp8_fp4_gemm_masked(dg_ctx* ctx, const dg_lp_operand* a, const int32_t* masked_m, const dg_lp_operand* b,
+                                     const dg_out* out, uint32_t num_groups, uint32_t expected_m, const dg_epilogue* epi);
+
+/* ops_sm100.rs:864 (fp8_fp4_bmm_dev): a (num_groups, m, k), b (num_groups, n, k); a.rows = m, b.rows = n. */
+int dg_fp8_fp4_bmm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, uint32_t num_groups,
+                   const dg_epilogue* epi);
+
+/* ops_sm100.rs:1091-1098 (sf_packed_cols, sf_aligned_rows) and the size of alloc_sf (:1107). */
+uint32_t dg_sf_packed_cols(uint32_t k, uint32_t gran_k);
+uint32_t dg_sf_aligned_rows(uint32_t rows);
+size_t dg_sf_words(uint32_t rows, uint32_t k, uint32_t gran_k, uint32_t num_groups);
+
+/* Scale selection rule of the FP4 quantiser.  0: the rule of the reference's CPU quantiser
+ * (deepgemm/src/reference.rs:273, exponent max(rounded, 128)); 1: smallest power of two that
+ * maps the block maximum into [-6, 6]. */
+enum { DG_SF_RULE_REFERENCE_CPU = 0, DG_SF_RULE_RANGE_FIT = 1 };
+
+/* ops_sm100.rs:1186 (cast_bf16_to_fp8_sf_dev).  Outputs are caller-allocated: dst rows*k bytes,
+ * sf dg_sf_words(rows, k, gran_k, num_groups) words (every word is written, no pre-zeroing needed
+ * except for the alignment padding rows, which are left untouched). */
+int dg_cast_bf16_to_fp8_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran_k,
+                           uint32_t num_groups, uint8_t* dst, uint32_t* sf);
+/* ops_sm100.rs:1135 (cast_bf16_to_fp4_packed_sf_dev): dst rows*k/2 bytes. */
+int dg_cast_bf16_to_fp4_packed_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
+                                  int sf_rule, uint8_t* dst, uint32_t* sf);
+
+/* deepgemm/src/ops.rs:52 (transform_sf_dev): (batches, mn, sf_k) f32 -> (batches*sf_k, align4(mn)) f32. */
+int dg_transform_sf(dg_ctx* ctx, const float* sf, uint32_t mn, uint32_t sf_k, uint32_t num_batches, float* dst);
+/* ops_sm100.rs:1250 / :1294 / :1372 (transform_sf{1d,2d,_t}_packed_ue8m0_dev) */
+int dg_transform_sf1d_packed_ue8m0(dg_ctx* ctx, const float* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran_k,
+                                   uint32_t num_groups, uint32_t* dst);
+int dg_transform_sf2d_packed_ue8m0(dg_ctx* ctx, const float* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
+                                   uint32_t* dst);
+int dg_transform_sf_t_packed_ue8m0(dg_ctx* ctx, const float* src, uint32_t rows, uint32_t k, uint32_t gran_k, uint32_t num_groups,
+                                   uint32_t* dst);
+/* ops_sm100.rs:1073 (run_psum_kernel): group_ends[g] = 1 + last row with m_indices == g; a group
+ * without rows takes the previous group's end. */
+int dg_group_ends_from_m_indices(dg_ctx* ctx, const int32_t* m_indices, uint32_t m, uint32_t num_groups, uint32_t* group_ends);
+/* ops_sm100.rs:1338 (unpack_fp4_raw_dev) */
+int dg_unpack_fp4_raw(dg_ctx* ctx, const uint8_t* src, size_t packed_len, uint8_t* dst);
+
+/* deepgemm/src/types.rs:195-219 (mk alignment knob; process-global, power of two in [16,256]). */
+int dg_set_mk_alignment_for_contiguous_layout(uint32_t value);
+uint32_t dg_get_mk_alignment_for_contiguous_layout(void);
+uint32_t dg_get_theoretical_mk_alignment_for_contiguous_layout(uint32_t arch_major);
+
+/* deepgemm/src/heuristics_sm100.rs:61-87 (Sm100Desc) and :17-57 (Sm100Layout/Storage/Config). */
+enum { DG_GEMM_NORMAL = 0, DG_GEMM_M_GROUPED_CONTIGUOUS = 1, DG_GEMM_M_GROUPED_MASKED = 2, DG_GEMM_BATCHED = 3 };
+typedef struct {
+    uint32_t gemm_type;
+    uint32_t m, n, k, num_groups, expected_m;
+    uint32_t a_bits, b_bits;
+    uint32_t gran_a, gran_b;
+    uint32_t cd_dtype;   /* DG_OUT_* */
+    uint32_t num_sms;
+} dg_desc;
+typedef struct {
+    uint32_t swap_ab;            /* always 0: A rows ride the UMMA M dimension */
+    uint32_t block_m, block_n, block_k;
+    uint32_t cluster_m, cluster_n;
+    uint32_t num_stages;
+    uint32_t num_accum_stages;   /* TMEM accumulator buffers (2 = epilogue overlaps the next tile) */
+    uint32_t smem_size;
+    uint32_t num_tiles;          /* expected tiles (from expected_m for grouped layouts) */
+} dg_config;
+/* heuristics_sm100.rs:455 (best_config) */
+int dg_best_config(const dg_desc* desc, dg_config* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DGB200_H_ */

@@ -262,6 +262,31 @@ DGO_API void dgo_cast_bf16_to_fp8_sf(const uint16_t* src, uint32_t ld, uint32_t 
     }
 }
 
+/* bf16 -> e4m3 with one UE8M0 exponent per block_rows x 128 block (block_rows = 128 is the
+ * weight recipe whose scales reference.rs:105 indexes per 128-row tile).  Same exponent rule
+ * as dgo_cast_bf16_to_fp8_sf (parity unpinned).  exps: (ceil(rows/block_rows), k/128) bytes. */
+DGO_API void dgo_quantize_fp8_ue8m0_blocks(const uint16_t* src, uint32_t ld, uint32_t rows, uint32_t k,
+                                           uint32_t block_rows, uint8_t* dst, uint8_t* exps) {
+    uint32_t kb_n = k / 128, rb_n = (rows + block_rows - 1) / block_rows;
+    #pragma omp parallel for schedule(static)
+    for (long rb = 0; rb < (long)rb_n; ++rb)
+        for (uint32_t kb = 0; kb < kb_n; ++kb) {
+            uint32_t r0 = (uint32_t)rb * block_rows, r1 = r0 + block_rows < rows ? r0 + block_rows : rows;
+            float amax = 0.0f;
+            for (uint32_t r = r0; r < r1; ++r)
+                for (uint32_t c = kb * 128; c < kb * 128 + 128; ++c) {
+                    float a = fabsf(dgo_bf16_to_f32(src[(size_t)r * ld + c]));
+                    if (a > amax) amax = a;
+                }
+            uint32_t e = dgo_sf_exp_e4m3(amax);
+            float inv = sf_inv(e);
+            exps[(size_t)rb * kb_n + kb] = (uint8_t)e;
+            for (uint32_t r = r0; r < r1; ++r)
+                for (uint32_t c = kb * 128; c < kb * 128 + 128; ++c)
+                    dst[(size_t)r * k + c] = dgo_f32_to_e4m3_fast(dgo_bf16_to_f32(src[(size_t)r * ld + c]) * inv);
+        }
+}
+
 /* The f32-scale recipe of the CPU-runnable case (parity unpinned): sf =
  * amax/448 (amax == 0 -> 1), q = e4m3(v / sf); blocks of block_rows x 128
  * (1 for activations, 128 for weights), scales laid out

@@ -47,6 +47,7 @@ _cast_fp4 = _sig("dgo_cast_bf16_to_fp4_packed_sf", None, _u16p, C.c_uint32, C.c_
                  C.c_uint32, C.c_int, _u8p, _u32p)
 _cast_fp8 = _sig("dgo_cast_bf16_to_fp8_sf", None, _u16p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                  C.c_uint32, _u8p, _u32p)
+_quant_blocks = _sig("dgo_quantize_fp8_ue8m0_blocks", None, _u16p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _u8p, _u8p)
 _quant_f32scale = _sig("dgo_quantize_fp8_f32scale", None, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, _u8p, _f32p)
 _tsf1d = _sig("dgo_transform_sf1d_packed", None, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
               C.c_uint32, _u32p)
@@ -169,6 +170,21 @@ def cast_bf16_to_fp8_sf(src_bits, k, gran, groups=1):
     sf = np.zeros(sf_words(rows, k, gran, groups), np.uint32)
     _cast_fp8(src_bits, ld, rows, k, gran, groups, dst, sf)
     return dst, sf
+
+
+def quantize_fp8_ue8m0_blocks(src_bits, k, block_rows):
+    """bf16 -> e4m3 with one UE8M0 exponent per (block_rows x 128) block; returns (bytes, exponents)."""
+    src_bits = np.ascontiguousarray(src_bits, dtype=np.uint16)
+    rows, ld = src_bits.shape
+    dst = np.zeros((rows, k), np.uint8)
+    exps = np.zeros(((rows + block_rows - 1) // block_rows, k // 128), np.uint8)
+    _quant_blocks(src_bits, ld, rows, k, block_rows, dst, exps)
+    return dst, exps
+
+
+def exps_to_f32(exps):
+    """UE8M0 bytes -> f32 powers of two (reference.rs:260-262)."""
+    return (np.ascontiguousarray(exps, np.uint8).astype(np.uint32) << 23).view(np.float32)
 
 
 def quantize_fp8_f32scale(x, block_rows):

@@ -1,0 +1,345 @@
+"""Parity of the tcgen05 GEMM family with the CPU oracle, through the C ABI.
+
+Tolerance: calc_diff = 1 - 2*sum(xy)/sum(x^2+y^2) <= 1e-3 is the contract; both sides compute
+the same quantised products, so the tests also hold the kernel to a much tighter internal bound
+(bf16 rounding of the output is the only expected difference).
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import deepgemm_rust_b200 as dg
+from oracle import oracle as O
+from tests.helpers import dev, fp4_operand, fp8_operand_1d, fp8_operand_2d, sample_indices, to_f32
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3          # contract
+TIGHT_BF16 = 2e-5   # what identical quantised inputs should give with a bf16 output
+TIGHT_F32 = 1e-6
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = dg.DgContext(0)
+    yield c
+    c.sync()
+    c.close()
+
+
+def lp(q, sf, rows, k, bits=8, gran=128):
+    return dg.LpOperand(dev(q), dev(sf), rows, k, k, bits, gran)
+
+
+def check_sampled(d, a, a_meta, b, b_meta, k, rows, cols, tight, d_rows=None):
+    """d: numpy f32 (all rows, n); compare d[d_rows][:, cols] with the oracle on operand rows `rows`."""
+    aq, asf, abits, agran, agroups, agr = a_meta
+    bq, bsf, bbits, bgran, bgroups, bgr = b_meta
+    want = O.lp_gemm_rows(aq, asf, abits, agran, agroups, agr, rows, bq, bsf, bbits, bgran, bgroups, bgr, cols, k)
+    got = d[np.asarray(rows if d_rows is None else d_rows, dtype=np.int64)][:, np.asarray(cols, dtype=np.int64) % d.shape[1]]
+    diff = O.calc_diff(got, want)
+    assert diff <= TOL, diff
+    assert diff <= tight, diff
+    return diff
+
+
+def run_dense(ctx, m, n, k, gran=128, out_kind=0, alpha=None, seed=0, b_tile_scales=True):
+    _, aq, asf = fp8_operand_1d(m, k, 1000 + seed, gran)
+    if b_tile_scales and gran == 128 and n % 128 == 0:
+        _, bq, bsf, _ = fp8_operand_2d(n, k, 2000 + seed)
+    else:
+        _, bq, bsf = fp8_operand_1d(n, k, 2000 + seed, gran)
+    dtype = torch.bfloat16 if out_kind == 0 else torch.float32
+    d = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+    out = dg.Sm100Out(out_kind, d, n)
+    dg.fp8_fp4_gemm_dev(ctx, lp(aq, asf, m, k, 8, gran), lp(bq, bsf, n, k, 8, gran), out, dg.Sm100Epilogue(alpha=alpha))
+    ctx.sync()
+    dn = to_f32(d)
+    assert not np.isnan(dn).any()
+    rows, cols = sample_indices(m, 48, seed), sample_indices(n, 64, seed + 1)
+    if alpha is not None:
+        dn = dn / np.float32(alpha)
+    return check_sampled(dn, aq, (aq, asf, 8, gran, 1, m), bq, (bq, bsf, 8, gran, 1, n), k, rows, cols,
+                         TIGHT_BF16 if out_kind == 0 else TIGHT_F32)
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 256, 512),      # the CPU-runnable case's shape
+    (256, 512, 768),      # reference e2e shape (tests/e2e.rs:47)
+    (128, 128, 128),      # one tile, one k-block
+    (100, 192, 640),      # ragged M, 5 k-blocks (scale word with a 1-byte tail)
+    (384, 2112, 1024),    # N not a multiple of the tile width
+    (1, 64, 256), (129, 72, 384),
+])
+def test_dense_fp8_small(ctx, m, n, k):
+    run_dense(ctx, m, n, k)
+
+
+def test_dense_fp8_matches_scalar_reference_and_golden(ctx):
+    # the committed fixture holds quantised inputs of the 128x256x512 case and the output of the scalar
+    # restatement of ref_fp8_gemm_nt (f32); the GPU f32 output must agree with it
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "fp8_gemm_128x256x512.npz"))
+    aq, bq, asf, bsf, want = z["a"], z["b"], z["a_sf_packed"], z["b_sf_packed"], z["out"]
+    d = torch.zeros((128, 256), dtype=torch.float32, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, lp(aq, asf, 128, 512), lp(bq, bsf, 256, 512), dg.Sm100Out.F32(d, 256))
+    ctx.sync()
+    diff = O.calc_diff(to_f32(d), want)
+    assert diff <= TIGHT_F32, diff
+
+
+@pytest.mark.parametrize("gran", [32])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (200, 320, 1152)])
+def test_dense_fp8_gran32(ctx, m, n, k, gran):
+    run_dense(ctx, m, n, k, gran=gran)
+
+
+def test_dense_f32_and_alpha(ctx):
+    run_dense(ctx, 256, 384, 1024, out_kind=1)
+    run_dense(ctx, 256, 384, 1024, out_kind=0, alpha=0.125)
+    run_dense(ctx, 128, 96, 512, out_kind=1, alpha=3.0)
+
+
+@pytest.mark.parametrize("m", [128, 4096])
+@pytest.mark.parametrize("n,k", [(2112, 7168), (24576, 1536), (7168, 16384), (4096, 7168), (7168, 2048)])
+def test_dense_fp8_full_size_sampled(ctx, m, n, k):
+    # full benchmark shapes: operands quantised on the GPU (bit-exactness of that kernel is its own test),
+    # outputs compared with the oracle on sampled rows / columns including every kind of tile edge
+    g = torch.Generator(device="cuda").manual_seed(1000 + n + k)
+    a = torch.randn((m, k), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    b = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    aq, asf = dg.cast_bf16_to_fp8_sf_dev(ctx, a, k, m, k, 128)
+    bq, bsf = dg.cast_bf16_to_fp8_sf_dev(ctx, b, k, n, k, 128)
+    d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, dg.LpOperand(aq, asf, m, k, k), dg.LpOperand(bq, bsf, n, k, k), dg.Sm100Out.Bf16(d, n))
+    ctx.sync()
+    assert not torch.isnan(d).any()
+    rows, cols = sample_indices(m, 24, n), sample_indices(n, 48, k)
+    aqn, asfn = aq[torch.from_numpy(rows.astype(np.int64)).cuda()].cpu().numpy(), asf.cpu().numpy().view(np.uint32)
+    bqn, bsfn = bq[torch.from_numpy(cols.astype(np.int64)).cuda()].cpu().numpy(), bsf.cpu().numpy().view(np.uint32)
+    # dequantise only the sampled rows: gather their scale words into a compact layout first
+    def compact(sf_words, total_rows, idx):
+        cols_n = dg.sf_packed_cols(k, 128)
+        w = sf_words.reshape(cols_n, dg.sf_aligned_rows(total_rows))[:, idx]
+        out = np.zeros((cols_n, dg.sf_aligned_rows(len(idx))), np.uint32)
+        out[:, :len(idx)] = w
+        return out.reshape(-1)
+    ar = np.arange(len(rows), dtype=np.uint32)
+    br = np.arange(len(cols), dtype=np.uint32)
+    want = O.lp_gemm_rows(aqn, compact(asfn, m, rows), 8, 128, 1, len(rows), ar, bqn, compact(bsfn, n, cols), 8, 128, 1, len(cols), br, k)
+    got = to_f32(d[torch.from_numpy(rows.astype(np.int64)).cuda()][:, torch.from_numpy(cols.astype(np.int64)).cuda()])
+    diff = O.calc_diff(got, want)
+    assert diff <= TIGHT_BF16, diff
+
+
+def contiguous_layout(group_sizes, alignment=128):
+    starts, m_idx = [], []
+    pos = 0
+    for g, s in enumerate(group_sizes):
+        starts.append(pos)
+        m_idx += [g] * s
+        pad = (-s) % alignment
+        m_idx += [-1] * pad
+        pos += s + pad
+    return np.array(m_idx, np.int32), starts
+
+
+@pytest.mark.parametrize("sizes,n,k", [
+    ([128, 128, 128, 128], 256, 512),           # reference e2e shape (tests/e2e.rs:439-500)
+    ([37, 128, 1, 64, 15, 100, 128, 3], 384, 1024),
+    ([200, 0, 300, 0, 0, 129], 512, 768),       # empty experts, multi-tile experts
+])
+def test_m_grouped_contiguous(ctx, sizes, n, k):
+    groups = len(sizes)
+    m_idx, starts = contiguous_layout(sizes)
+    m_total = len(m_idx)
+    _, aq, asf = fp8_operand_1d(m_total, k, 11)
+    _, bq, bsf, sfb_tiles = fp8_operand_2d(groups * n, k, 12, groups)
+    d = torch.full((m_total, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    a_op = lp(aq, asf, m_total, k)
+    b_op = lp(bq, bsf, groups * n, k)
+    dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a_op, dev(m_idx), b_op, dg.Sm100Out.Bf16(d, n), groups)
+    ctx.sync()
+    dn = to_f32(d)
+    valid = np.nonzero(m_idx >= 0)[0]
+    assert not np.isnan(dn[valid]).any()
+    # the scalar restatement of ref_m_grouped_fp8_gemm_nt_contiguous on every valid row (per-expert tile scales)
+    kb = k // 128
+    sfa = np.stack([O.exps_to_f32(((asf.reshape(-1, dg.sf_aligned_rows(m_total))[c // 4] >> ((c % 4) * 8)) & 0xFF).astype(np.uint8))
+                    for c in range(kb)], axis=1)[:m_total]
+    want = O.ref_m_grouped_contiguous(aq, sfa, m_idx, bq, sfb_tiles.reshape(-1), n, per_group_sfb=True, threads=8)
+    diff = O.calc_diff(dn[valid], want[valid])
+    assert diff <= TIGHT_BF16, diff
+    # the prebuilt-table entry point gives the same bytes
+    d2 = torch.zeros_like(d)
+    ends = dg.psum_from_m_indices_dev(ctx, dev(m_idx), groups)
+    dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, b_op, dg.Sm100Out.Bf16(d2, n), groups)
+    ctx.sync()
+    assert torch.equal(d[torch.from_numpy(valid).cuda()], d2[torch.from_numpy(valid).cuda()])
+
+
+@pytest.mark.parametrize("masked,m_max,n,k", [
+    ([37, 128, 1, 64, 15, 100, 128, 3], 128, 256, 512),   # reference fixture (tests/e2e.rs:131,566)
+    ([0, 256, 17, 129, 255, 16, 0, 1], 256, 384, 1024),
+    ([100, 7], 100, 128, 256),                               # m_max not a multiple of the tile
+])
+def test_m_grouped_masked(ctx, masked, m_max, n, k):
+    groups = len(masked)
+    masked_m = np.array(masked, np.int32)
+    _, aq, asf = fp8_operand_1d(groups * m_max, k, 21, 128, groups)
+    _, bq, bsf, sfb_tiles = fp8_operand_2d(groups * n, k, 22, groups)
+    d = torch.full((groups * m_max, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, lp(aq, asf, m_max, k), dev(masked_m), lp(bq, bsf, groups * n, k),
+                                         dg.Sm100Out.Bf16(d, n), groups, max(1, int(masked_m.mean())))
+    ctx.sync()
+    dn = to_f32(d)
+    kb = k // 128
+    stride = dg.sf_aligned_rows(m_max)
+    cols = dg.sf_packed_cols(k, 128)
+    sfa = np.zeros((groups * m_max, kb), np.float32)
+    w = asf.reshape(groups, cols, stride)
+    for c in range(kb):
+        sfa[:, c] = O.exps_to_f32(((w[:, c // 4, :m_max] >> ((c % 4) * 8)) & 0xFF).astype(np.uint8)).reshape(-1)
+    want = O.ref_m_grouped_masked(aq, sfa, masked_m, m_max, bq, sfb_tiles.reshape(-1), n, per_group_sfb=True, threads=8)
+    valid = np.concatenate([np.arange(g * m_max, g * m_max + masked[g]) for g in range(groups)]).astype(np.int64)
+    assert not np.isnan(dn[valid]).any()
+    diff = O.calc_diff(dn[valid], want[valid])
+    assert diff <= TIGHT_BF16, diff
+    # rows of a group whose tiles were never scheduled keep the caller's contents (no stray writes)
+    for g in range(groups):
+        first_untouched = g * m_max + ((masked[g] + 127) // 128) * 128
+        if first_untouched < (g + 1) * m_max:
+            assert np.isnan(dn[first_untouched:(g + 1) * m_max]).all()
+
+
+def test_bmm_and_fp8_requant_epilogue(ctx):
+    groups, m, n, k = 3, 160, 256, 512
+    _, aq, asf = fp8_operand_1d(groups * m, k, 31, 128, groups)
+    _, bq, bsf = fp8_operand_1d(groups * n, k, 32, 128, groups)
+    a_op, b_op = lp(aq, asf, m, k), lp(bq, bsf, n, k)
+    d32 = torch.zeros((groups * m, n), dtype=torch.float32, device="cuda")
+    dg.fp8_fp4_bmm_dev(ctx, a_op, b_op, dg.Sm100Out.F32(d32, n), groups)
+    ctx.sync()
+    dn = to_f32(d32)
+    for g in range(groups):
+        rows = np.arange(g * m, (g + 1) * m, dtype=np.uint32)
+        colsb = np.arange(g * n, (g + 1) * n, dtype=np.uint32)
+        want = O.lp_gemm_rows(aq, asf, 8, 128, groups, m, rows, bq, bsf, 8, 128, groups, n, colsb, k)
+        assert O.calc_diff(dn[g * m:(g + 1) * m], want) <= TIGHT_F32
+    # FP8 output: the same accumulators, rounded to bf16, scaled per 32 columns, cast to e4m3.  The CPU
+    # epilogue applied to the GPU's own f32 output must give the identical bytes and scale words.
+    d8 = torch.zeros((groups * m, n), dtype=torch.uint8, device="cuda")
+    sfd = torch.zeros(groups * (n // 128) * dg.sf_aligned_rows(m), dtype=torch.int32, device="cuda")
+    dg.fp8_fp4_bmm_dev(ctx, a_op, b_op, dg.Sm100Out.Fp8(d8, n, sfd), groups)
+    ctx.sync()
+    want8 = np.zeros((groups * m, n), np.uint8)
+    want_sfd = np.zeros(sfd.numel(), np.uint32)
+    for g in range(groups):
+        O.requant_fp8(dn[g * m:(g + 1) * m], g, dg.sf_aligned_rows(m), want8[g * m:(g + 1) * m], want_sfd)
+    assert np.array_equal(d8.cpu().numpy(), want8)
+    assert np.array_equal(sfd.cpu().numpy().view(np.uint32), want_sfd)
+
+
+def test_masked_fp8_requant_feeds_next_gemm(ctx):
+    # decode-style: masked GEMM with FP8 output whose D/SFD are directly the next masked GEMM's operand (gran 32)
+    groups, m_max, n, k = 4, 128, 512, 1024
+    masked_m = np.array([128, 5, 0, 77], np.int32)
+    _, aq, asf = fp8_operand_1d(groups * m_max, k, 41, 128, groups)
+    _, bq, bsf, _ = fp8_operand_2d(groups * n, k, 42, groups)
+    a_op, b_op = lp(aq, asf, m_max, k), lp(bq, bsf, groups * n, k)
+    d32 = torch.zeros((groups * m_max, n), dtype=torch.float32, device="cuda")
+    dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, a_op, dev(masked_m), b_op, dg.Sm100Out.F32(d32, n), groups, 64)
+    d8 = torch.zeros((groups * m_max, n), dtype=torch.uint8, device="cuda")
+    sfd = torch.zeros(groups * (n // 128) * m_max, dtype=torch.int32, device="cuda")
+    dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, a_op, dev(masked_m), b_op, dg.Sm100Out.Fp8(d8, n, sfd), groups, 64)
+    ctx.sync()
+    dn = to_f32(d32)
+    got8, got_sfd = d8.cpu().numpy(), sfd.cpu().numpy().view(np.uint32).reshape(groups, n // 128, m_max)
+    for g in range(groups):
+        v = int(masked_m[g])
+        if v == 0:
+            continue
+        want8 = np.zeros((v, n), np.uint8)
+        want_sfd = np.zeros(groups * (n // 128) * m_max, np.uint32)
+        O.requant_fp8(dn[g * m_max:g * m_max + v], g, m_max, want8, want_sfd)
+        assert np.array_equal(got8[g * m_max:g * m_max + v], want8)
+        assert np.array_equal(got_sfd[g, :, :v], want_sfd.reshape(groups, n // 128, m_max)[g, :, :v])
+    # second GEMM consumes (d8, sfd) as an e4m3 operand with per-32 scales
+    n2 = 256
+    _, wq, wsf = fp8_operand_1d(groups * n2, n, 43, 32, groups)
+    d2 = torch.zeros((groups * m_max, n2), dtype=torch.bfloat16, device="cuda")
+    a2 = dg.LpOperand(d8, sfd, m_max, n, n, 8, 32)
+    dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, a2, dev(masked_m), lp(wq, wsf, groups * n2, n, 8, 32), dg.Sm100Out.Bf16(d2, n2), groups, 64)
+    ctx.sync()
+    d2n = to_f32(d2)
+    for g in range(groups):
+        v = int(masked_m[g])
+        if v == 0:
+            continue
+        rows = np.arange(g * m_max, g * m_max + v, dtype=np.uint32)
+        colsb = np.arange(g * n2, (g + 1) * n2, dtype=np.uint32)
+        want = O.lp_gemm_rows(got8, sfd.cpu().numpy().view(np.uint32), 8, 32, groups, m_max, rows, wq, wsf, 8, 32, groups, n2, colsb, n)
+        assert O.calc_diff(d2n[g * m_max:g * m_max + v], want) <= TIGHT_BF16
+
+
+@pytest.mark.parametrize("m,n,k,rule", [(128, 256, 512, 0), (256, 512, 768, 1), (8, 8, 128, 0), (200, 192, 1280, 1)])
+def test_dense_mxfp4(ctx, m, n, k, rule):
+    # reference e2e MXFP4 shapes (tests/e2e.rs:266-350) against mxfp4_gemm_reference (reference.rs:293-329)
+    _, aq, asf = fp4_operand(m, k, 51, 1, rule)
+    _, bq, bsf = fp4_operand(n, k, 52, 1, rule)
+    d = torch.zeros((m, n), dtype=torch.float32, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, dg.LpOperand(dev(aq), dev(asf), m, k, k, 4, 32), dg.LpOperand(dev(bq), dev(bsf), n, k, k, 4, 32),
+                        dg.Sm100Out.F32(d, n))
+    ctx.sync()
+    want = O.mxfp4_gemm_reference(aq, asf, m, bq, bsf, n, k, threads=8)
+    assert O.calc_diff(to_f32(d), want) <= TIGHT_F32
+
+
+def test_m_grouped_mxfp4(ctx):
+    groups, gm, n, k = 4, 128, 256, 512     # tests/e2e.rs:439-500
+    _, aq, asf = fp4_operand(groups * gm, k, 61, 1, 1)
+    _, bq, bsf = fp4_operand(groups * n, k, 62, groups, 1)
+    m_idx = np.repeat(np.arange(groups, dtype=np.int32), gm)
+    d = torch.zeros((groups * gm, n), dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(dev(aq), dev(asf), groups * gm, k, k, 4, 32), dev(m_idx),
+                                             dg.LpOperand(dev(bq), dev(bsf), groups * n, k, k, 4, 32), dg.Sm100Out.Bf16(d, n), groups)
+    ctx.sync()
+    dn = to_f32(d)
+    for g in range(groups):
+        rows = np.arange(g * gm, (g + 1) * gm, dtype=np.uint32)
+        colsb = np.arange(g * n, (g + 1) * n, dtype=np.uint32)
+        want = O.lp_gemm_rows(aq, asf, 4, 32, 1, groups * gm, rows, bq, bsf, 4, 32, groups, n, colsb, k)
+        assert O.calc_diff(dn[g * gm:(g + 1) * gm], want) <= TIGHT_BF16
+
+
+def test_argument_errors(ctx):
+    _, aq, asf = fp8_operand_1d(128, 512, 1)
+    _, bq, bsf = fp8_operand_1d(128, 512, 2)
+    a, b = lp(aq, asf, 128, 512), lp(bq, bsf, 128, 512)
+    d = torch.zeros((128, 128), dtype=torch.bfloat16, device="cuda")
+    out = dg.Sm100Out.Bf16(d, 128)
+
+    def kind(fn):
+        with pytest.raises(dg.DgError) as e:
+            fn()
+        return e.value.kind
+
+    d8 = torch.zeros((128, 128), dtype=torch.uint8, device="cuda")
+    sfd = torch.zeros(128, dtype=torch.int32, device="cuda")
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.Fp8(d8, 128, sfd))) == "Shape"      # ops_sm100.rs:727
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, out, dg.Sm100Epilogue(alpha=2.0, accumulate=True))) == "Shape"  # :150
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, out, dg.Sm100Epilogue(accumulate=True))) == "Unsupported"
+    bad = dg.LpOperand(a.data, a.sf, 128, 512, 512, 8, 64)
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, bad, b, out)) == "Shape"                               # :52
+    bad = dg.LpOperand(a.data, a.sf, 256, 512, 512)
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, bad, b, dg.Sm100Out.Bf16(torch.zeros((256, 128), dtype=torch.bfloat16, device="cuda"), 128))) == "Shape"  # :71
+    bad = dg.LpOperand(a.data, a.sf, 128, 384, 512)
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, bad, b, out)) == "Shape"                               # k mismatch
+    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.Bf16(d, 64))) == "Shape"             # ld < n
+    assert kind(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, dev(np.zeros(128, np.int32)), b, out, 3)) == "Shape"
+    dg.set_mk_alignment_for_contiguous_layout(64)
+    try:
+        assert kind(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, dev(np.zeros(128, np.int32)), b, out, 1)) == "Unsupported"
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+    ctx.sync()

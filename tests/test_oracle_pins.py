@@ -285,3 +285,18 @@ def test_lcg_generator_matches_reference_recurrence():
         s = (s * 6364136223846793005 + 1442695040888963407) % 2 ** 64
         assert v[i] == (np.float32(s >> 33) / np.float32(4294967295.0) - np.float32(0.5)) * np.float32(2.0)
     assert np.all(np.abs(v) <= 1.0)
+
+
+def test_golden_fixtures_reproduce():
+    # the committed vectors (tests/golden/make_golden.py) are what the oracle computes today
+    import os
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    z = np.load(os.path.join(here, "fp8_gemm_128x256x512.npz"))
+    assert np.array_equal(O.ref_fp8_gemm_nt(z["a"], z["sfa"], z["b"], z["sfb"]), z["out"])
+    assert np.array_equal(O.transform_sf1d_packed(z["sfa"], 512, 128), z["a_sf_packed"])
+    assert np.array_equal(O.transform_sf2d_packed(z["sfb"], 256, 512), z["b_sf_packed"])
+    a_bits = O.bf16_bits(np.random.default_rng(1001).standard_normal((128, 512)).astype(np.float32))
+    aq, a_exp = O.quantize_fp8_ue8m0_blocks(a_bits, 512, 1)
+    assert np.array_equal(aq, z["a"]) and np.array_equal(O.exps_to_f32(a_exp), z["sfa"])
+    z = np.load(os.path.join(here, "mxfp4_8x8x128.npz"))
+    assert np.array_equal(O.mxfp4_gemm_reference(z["a"], z["a_sf"], 8, z["b"], z["b_sf"], 8, 128), z["out"])
