@@ -179,46 +179,63 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
     const uint32_t groups = d->num_groups ? d->num_groups : 1;
     const uint32_t sfa_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
     const uint32_t sfb_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
-    const uint32_t step = d->cd_dtype == DG_OUT_FP8 ? 128 : (d->cd_dtype == DG_OUT_F32 ? 32 : 64);
-    uint32_t m_blocks;
-    if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) m_blocks = ceil_div(d->m, 128);
-    else if (d->gemm_type == DG_GEMM_M_GROUPED_MASKED) m_blocks = groups * ceil_div(d->expected_m ? d->expected_m : d->m, 128);
-    else m_blocks = groups * ceil_div(d->m, 128);
-
-    uint32_t best_n = 0, best_accum = 0, best_tiles = 0;
-    double best_cost = 0;
-    const char* force = getenv("DG_BLOCK_N");
-    for (uint32_t bn = step; bn <= 256; bn += step) {
-        if (bn % 16 != 0) continue;
-        if (force && static_cast<uint32_t>(atoi(force)) != bn) continue;
-        const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
-        const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
-        if (bn + sf_cols > 512) continue;
-        const uint32_t tiles = m_blocks * ceil_div(d->n, bn);
-        const uint32_t waves = ceil_div(tiles, sms);
-        // per-tile time ~ the wider of the MMA (bn) and the shared-memory traffic of the A tile (~ 96),
-        // plus the part of the epilogue that cannot hide behind the next tile
-        const double k_blocks = ceil_div(d->k, block_k);
-        const double tile_cost = k_blocks * (bn > 96 ? bn : 96) + (accum == 1 ? 6.0 * bn : 0.5 * bn) + 300.0;
-        const double cost = waves * tile_cost;
-        if (best_n == 0 || cost < best_cost - 1e-9) { best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; }
-    }
-    if (best_n == 0) return fail(DG_ERR_SHAPE, "no tile configuration fits (DG_BLOCK_N=%s)", force ? force : "");
-    uint32_t stages = dg::kMaxStages;
+    const uint32_t step = d->cd_dtype == DG_OUT_FP8 ? 128 : 32;
+    const uint32_t align = g_mk_alignment.load();
+    const char* force_n = getenv("DG_BLOCK_N");
+    const char* force_ctas = getenv("DG_CTAS");
     const char* force_stages = getenv("DG_STAGES");
-    if (force_stages) stages = static_cast<uint32_t>(atoi(force_stages));
-    while (stages > 1 && dg::gemm_smem_bytes(best_n, stages, sfa_words, sfb_words) > kSmemCapacity) --stages;
-    if (stages < 1 || stages > dg::kMaxStages || dg::gemm_smem_bytes(best_n, stages, sfa_words, sfb_words) > kSmemCapacity)
-        return fail(DG_ERR_SHAPE, "no pipeline depth fits in shared memory");
+
+    uint32_t best_n = 0, best_accum = 0, best_tiles = 0, best_ctas = 0, best_stages = 0;
+    double best_cost = 0;
+    for (uint32_t ctas = 1; ctas <= 2; ++ctas) {
+        if (force_ctas && static_cast<uint32_t>(atoi(force_ctas)) != ctas) continue;
+        const uint32_t tile_m = 128 * ctas;
+        // a CTA pair needs 256-row tiles that stay inside one group
+        if (ctas == 2 && d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS && align % 256 != 0) continue;
+        if (ctas == 2 && sms < 2) continue;
+        uint32_t m_blocks;
+        if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) m_blocks = ceil_div(d->m, tile_m);
+        else if (d->gemm_type == DG_GEMM_M_GROUPED_MASKED) m_blocks = groups * ceil_div(d->expected_m ? d->expected_m : d->m, tile_m);
+        else m_blocks = groups * ceil_div(d->m, tile_m);
+        const uint32_t workers = sms / ctas;
+        for (uint32_t bn = step; bn <= 256; bn += step) {
+            if (bn % (16 * ctas) != 0) continue;
+            if (force_n && static_cast<uint32_t>(atoi(force_n)) != bn) continue;
+            const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
+            if (bn + sf_cols > 512) continue;
+            const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
+            uint32_t stages = force_stages ? static_cast<uint32_t>(atoi(force_stages)) : dg::kMaxStages;
+            if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+            while (stages > 1 && dg::gemm_smem_bytes(bn, ctas, d->cd_dtype, stages, sfa_words, sfb_words) > kSmemCapacity) --stages;
+            if (stages < 1 || dg::gemm_smem_bytes(bn, ctas, d->cd_dtype, stages, sfa_words, sfb_words) > kSmemCapacity) continue;
+            if (stages < 3 && !force_stages) continue;
+            const uint32_t tiles = m_blocks * ceil_div(d->n, bn);
+            const uint32_t waves = ceil_div(tiles, workers);
+            // cycles per tile.  One UMMA (K = 32 bytes) costs max(~118, bn / 2) cycles on its CTA's tensor core
+            // (measured issue floor / 8192 MACs per cycle); the loads of a k-block (A 16 KB + B bn/ctas x 128 B)
+            // must also arrive, at roughly 64 bytes per cycle per SM when every SM streams from L2.
+            const double k_blocks = ceil_div(d->k, block_k);
+            const double mma = 4.0 * (bn * 0.5 > 118.0 ? bn * 0.5 : 118.0);
+            const double feed = (16384.0 + bn / ctas * 128.0) / 64.0;
+            const double epilogue = accum == 1 ? 9.0 * bn : 1.0 * bn;  // not hidden behind the next tile when single-buffered
+            const double tile_cost = k_blocks * (mma > feed ? mma : feed) + epilogue + 600.0;
+            const double cost = waves * tile_cost;
+            if (best_n == 0 || cost < best_cost * (1.0 - 1e-9)) {
+                best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; best_ctas = ctas; best_stages = stages;
+            }
+        }
+    }
+    if (best_n == 0) return fail(DG_ERR_SHAPE, "no tile configuration fits (DG_BLOCK_N=%s DG_CTAS=%s)", force_n ? force_n : "", force_ctas ? force_ctas : "");
+    const uint32_t stages = best_stages;
     out->swap_ab = 0;
-    out->block_m = 128;
+    out->block_m = 128 * best_ctas;
     out->block_n = best_n;
     out->block_k = block_k;
-    out->cluster_m = 1;
+    out->cluster_m = best_ctas;
     out->cluster_n = 1;
     out->num_stages = stages;
     out->num_accum_stages = best_accum;
-    out->smem_size = dg::gemm_smem_bytes(best_n, stages, sfa_words, sfb_words);
+    out->smem_size = dg::gemm_smem_bytes(best_n, best_ctas, d->cd_dtype, stages, sfa_words, sfb_words);
     out->num_tiles = best_tiles;
     return DG_OK;
 }
@@ -269,9 +286,9 @@ struct Problem {
     const uint32_t* layout;
 };
 
-template <bool kMXF4, uint32_t kOut>
+template <bool kMXF4, uint32_t kOut, uint32_t kCtas>
 cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
-    auto kernel = dg::dg_gemm_kernel<kMXF4, kOut>;
+    auto kernel = dg::dg_gemm_kernel<kMXF4, kOut, kCtas>;
     // the opt-in is per device; remember which devices already have it
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -281,8 +298,27 @@ cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem,
         if (e != cudaSuccess) return e;
         if (dev < 64) configured.fetch_or(1ull << dev);
     }
-    kernel<<<grid, dg::kNumThreads, smem, stream>>>(p, maps[0], maps[1], maps[2], maps[3], maps[4]);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(dg::kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kCtas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p, maps[0], maps[1], maps[2], maps[3], maps[4]);
+}
+
+template <bool kMXF4, uint32_t kCtas>
+cudaError_t launch_by_out(int kind, const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
+    if (kind == DG_OUT_BF16) return launch_kernel<kMXF4, dg::kOutBf16, kCtas>(p, grid, smem, stream, maps);
+    if (kind == DG_OUT_F32) return launch_kernel<kMXF4, dg::kOutF32, kCtas>(p, grid, smem, stream, maps);
+    return launch_kernel<kMXF4, dg::kOutFp8, kCtas>(p, grid, smem, stream, maps);
 }
 
 int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi, const Problem& pr) {
@@ -325,8 +361,9 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     if (rc) return rc;
     static const bool print_cfg = [] { const char* v = getenv("DG_PRINT_CONFIGS"); return v && strcmp(v, "0") != 0; }();
     if (print_cfg)
-        fprintf(stderr, "[dgb200] type=%u m=%u n=%u k=%u groups=%u -> block=128x%ux%u stages=%u accum=%u smem=%u tiles~%u\n", pr.type, pr.m, pr.n,
-                pr.k, pr.groups, cfg.block_n, cfg.block_k, cfg.num_stages, cfg.num_accum_stages, cfg.smem_size, cfg.num_tiles);
+        fprintf(stderr, "[dgb200] type=%u m=%u n=%u k=%u groups=%u -> block=%ux%ux%u ctas=%u stages=%u accum=%u smem=%u tiles~%u\n", pr.type, pr.m,
+                pr.n, pr.k, pr.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_m, cfg.num_stages, cfg.num_accum_stages, cfg.smem_size,
+                cfg.num_tiles);
 
     const bool mxf4 = a->bits == 4;
     const uint32_t block_k = cfg.block_k;
@@ -345,7 +382,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         if (rc) return rc;
         uint64_t bdims[3] = {pr.k, pr.n, b_groups};
         uint64_t bstrides[2] = {b_pitch, b_pitch * pr.n};
-        uint32_t bbox[3] = {block_k, cfg.block_n, 1};
+        uint32_t bbox[3] = {block_k, cfg.block_n / cfg.cluster_m, 1};
         rc = encode_map(&maps[1], dt, 3, b->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
         if (rc) return rc;
     }
@@ -368,8 +405,10 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         const uint64_t pitch = static_cast<uint64_t>(out->ld) * d_elem;
         uint64_t dims[3] = {pr.n, pr.m, a_groups};
         uint64_t strides[2] = {pitch, pitch * pr.m};
-        uint32_t box[3] = {128 / d_elem, 32, 1};
-        rc = encode_map(&maps[4], dt, 3, out->buf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "D");
+        // 32 rows per store; 32 columns of bf16 (64-byte rows) or f32, 128 columns of e4m3 (128-byte rows)
+        uint32_t box[3] = {out->kind == DG_OUT_FP8 ? 128u : 32u, 32, 1};
+        rc = encode_map(&maps[4], dt, 3, out->buf, dims, strides, box,
+                        out->kind == DG_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, "D");
         if (rc) return rc;
     }
 
@@ -395,19 +434,15 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.grouped_layout = pr.layout;
     p.status = ctx->status;
 
-    uint32_t grid = static_cast<uint32_t>(ctx->num_sms);
-    if (pr.type == DG_GEMM_NORMAL || pr.type == DG_GEMM_BATCHED) grid = cfg.num_tiles < grid ? cfg.num_tiles : grid;
+    const uint32_t ctas = cfg.cluster_m;
+    uint32_t grid = static_cast<uint32_t>(ctx->num_sms) / ctas * ctas;
+    if (pr.type == DG_GEMM_NORMAL || pr.type == DG_GEMM_BATCHED) grid = cfg.num_tiles * ctas < grid ? cfg.num_tiles * ctas : grid;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     cudaError_t ce;
-    if (mxf4) {
-        if (out->kind == DG_OUT_BF16) ce = launch_kernel<true, dg::kOutBf16>(p, grid, cfg.smem_size, ctx->stream, maps);
-        else if (out->kind == DG_OUT_F32) ce = launch_kernel<true, dg::kOutF32>(p, grid, cfg.smem_size, ctx->stream, maps);
-        else ce = launch_kernel<true, dg::kOutFp8>(p, grid, cfg.smem_size, ctx->stream, maps);
-    } else {
-        if (out->kind == DG_OUT_BF16) ce = launch_kernel<false, dg::kOutBf16>(p, grid, cfg.smem_size, ctx->stream, maps);
-        else if (out->kind == DG_OUT_F32) ce = launch_kernel<false, dg::kOutF32>(p, grid, cfg.smem_size, ctx->stream, maps);
-        else ce = launch_kernel<false, dg::kOutFp8>(p, grid, cfg.smem_size, ctx->stream, maps);
-    }
+    if (mxf4) ce = ctas == 2 ? launch_by_out<true, 2>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps)
+                             : launch_by_out<true, 1>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps);
+    else ce = ctas == 2 ? launch_by_out<false, 2>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps)
+                        : launch_by_out<false, 1>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps);
     if (ce != cudaSuccess) return fail(DG_ERR_DRIVER, "kernel launch failed: %s", cudaGetErrorString(ce));
     return DG_OK;
 }

@@ -85,11 +85,9 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
                 for (uint32_t i = 0; i < 8; ++i) s[i] = v[i] * inv;
                 *reinterpret_cast<uint32_t*>(p.dst + static_cast<size_t>(row) * (p.k / 2) + k0[h] / 2) = cvt_e2m1x8(s);
             } else {
-                // "+ 0.0f" turns an exact -0.0 product into +0.0: the oracle's encoder takes the
-                // sign from (v < 0), the hardware conversion would keep the sign bit
                 uint2 out;
-                out.x = cvt_e4m3x4(v[0] * inv + 0.0f, v[1] * inv + 0.0f, v[2] * inv + 0.0f, v[3] * inv + 0.0f);
-                out.y = cvt_e4m3x4(v[4] * inv + 0.0f, v[5] * inv + 0.0f, v[6] * inv + 0.0f, v[7] * inv + 0.0f);
+                out.x = cvt_e4m3x4(scale_pos_zero(v[0], inv), scale_pos_zero(v[1], inv), scale_pos_zero(v[2], inv), scale_pos_zero(v[3], inv));
+                out.y = cvt_e4m3x4(scale_pos_zero(v[4], inv), scale_pos_zero(v[5], inv), scale_pos_zero(v[6], inv), scale_pos_zero(v[7], inv));
                 *reinterpret_cast<uint2*>(p.dst + static_cast<size_t>(row) * p.k + k0[h]) = out;
             }
         }

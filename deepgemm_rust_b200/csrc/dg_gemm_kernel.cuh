@@ -7,9 +7,9 @@
 // blocks along K) and are applied by the tensor core itself (tcgen05.mma ... block_scale).
 //
 // Roles inside one 256-thread CTA (one CTA per SM, looping over output tiles):
-//   warp 0      lane 0 issues every TMA load: A/B tiles into a ring of 128B-swizzled stages,
+//   warp 0      issues every TMA load: A/B tiles into a ring of 128B-swizzled stages,
 //               scale-factor words into the same stage's raw scale area
-//   warp 1      allocates TMEM; lane 0 copies scales smem->TMEM (tcgen05.cp) and issues the
+//   warp 1      allocates TMEM; copies scales smem->TMEM (tcgen05.cp) and issues the
 //               UMMAs; tcgen05.commit releases the stage and, after the last k-block,
 //               publishes the accumulator
 //   warp 2      re-orders each 128-word scale chunk from row order to the 32x4 order the
@@ -17,6 +17,9 @@
 //   warp 3      idle
 //   warps 4-7   epilogue: TMEM -> registers -> {bf16 | f32 | e4m3 + UE8M0 row scales}
 //               -> swizzled staging -> TMA store; each warp owns 32 rows and stores on its own
+// With kCtas = 2 two CTAs of a cluster share one 256 x BLOCK_N tile (tcgen05 cta_group::2): each
+// loads its own 128 rows of A and half of the B rows, rank 0 issues the UMMAs for both, each
+// CTA's TMEM receives its own 128 accumulator rows and runs its own epilogue.
 // Accumulators are double-buffered in TMEM whenever 2*BLOCK_N plus the scale columns fit
 // in 512 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
 #pragma once
@@ -32,7 +35,8 @@ constexpr uint32_t kBlockKBytes = 128;     // one 128-byte swizzle row of K per 
 constexpr uint32_t kUmmaKBytes = 32;       // K bytes consumed by one UMMA
 constexpr uint32_t kMaxStages = 12;
 constexpr uint32_t kNumThreads = 256;
-constexpr uint32_t kEpilogueBufBytes = 4096;  // 32 rows x 128 bytes per warp per buffer
+// staging buffer of one epilogue warp: 32 rows x 64 bytes (bf16, 32 columns) or x 128 bytes (f32 / e4m3)
+constexpr uint32_t epilogue_buf_bytes(uint32_t out_kind) { return out_kind == 0 ? 2048u : 4096u; }
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {
@@ -61,11 +65,15 @@ struct Tile {
 // Walks the tile list of one CTA.  Every role runs its own copy and sees the same sequence.
 struct Scheduler {
     const GemmParams& p;
+    uint32_t tile_m, worker, num_workers;   // rows per tile; CTA (or CTA pair) index and count
     uint32_t num_m_blocks, num_n_blocks, iter;
     uint32_t cur_group, cum_begin, cur_m_blocks, cur_row_start;
 
-    DG_DEVICE explicit Scheduler(const GemmParams& params) : p(params) {
-        num_m_blocks = (p.m + kBlockM - 1) / kBlockM;
+    DG_DEVICE Scheduler(const GemmParams& params, uint32_t ctas) : p(params) {
+        tile_m = kBlockM * ctas;
+        worker = blockIdx.x / ctas;
+        num_workers = gridDim.x / ctas;
+        num_m_blocks = (p.m + tile_m - 1) / tile_m;
         num_n_blocks = (p.n + p.block_n - 1) / p.block_n;
         iter = 0;
         cur_group = 0;
@@ -82,17 +90,17 @@ struct Scheduler {
             const uint32_t end = __ldg(p.grouped_layout + cur_group);
             cur_row_start = (prev_end + p.mk_alignment - 1) / p.mk_alignment * p.mk_alignment;
             const uint32_t rows = end > cur_row_start ? end - cur_row_start : 0u;
-            cur_m_blocks = (rows + kBlockM - 1) / kBlockM;
+            cur_m_blocks = (rows + tile_m - 1) / tile_m;
         } else {
             const int32_t valid = static_cast<int32_t>(__ldg(p.grouped_layout + cur_group));
             const uint32_t rows = valid <= 0 ? 0u : (static_cast<uint32_t>(valid) < p.m ? static_cast<uint32_t>(valid) : p.m);
             cur_row_start = 0;
-            cur_m_blocks = (rows + kBlockM - 1) / kBlockM;
+            cur_m_blocks = (rows + tile_m - 1) / tile_m;
         }
     }
 
     DG_DEVICE bool next(Tile& t) {
-        const uint32_t idx = blockIdx.x + (iter++) * gridDim.x;
+        const uint32_t idx = worker + (iter++) * num_workers;
         if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmBatched) {
             const uint32_t per_group = num_m_blocks * num_n_blocks;
             if (idx >= per_group * p.num_groups) return false;
@@ -105,7 +113,7 @@ struct Scheduler {
             const uint32_t first_m = band * kBand;
             const uint32_t rows_here = num_m_blocks - first_m < kBand ? num_m_blocks - first_m : kBand;
             const uint32_t nb = in_band / rows_here, mb = first_m + (in_band - nb * rows_here);
-            t.m0 = mb * kBlockM;
+            t.m0 = mb * tile_m;
             t.n0 = nb * p.block_n;
             t.ga = t.gb = g;
             return true;
@@ -120,7 +128,7 @@ struct Scheduler {
         }
         const uint32_t in_group = idx - cum_begin;
         const uint32_t nb = in_group / cur_m_blocks, ml = in_group - nb * cur_m_blocks;
-        t.m0 = cur_row_start + ml * kBlockM;
+        t.m0 = cur_row_start + ml * tile_m;
         t.n0 = nb * p.block_n;
         t.gb = cur_group;
         t.ga = p.gemm_type == kGemmContiguous ? 0u : cur_group;
@@ -142,21 +150,26 @@ DG_DEVICE SfPlan sf_plan(uint32_t gran, uint32_t block_k_elems) {
     return s;
 }
 
-template <bool kMXF4, uint32_t kOut>
+template <bool kMXF4, uint32_t kOut, uint32_t kCtas>
 __global__ void __launch_bounds__(kNumThreads, 1)
 dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                const __grid_constant__ CUtensorMap tmap_d) {
     constexpr uint32_t kBlockKElems = kMXF4 ? 256 : 128;
+    constexpr uint32_t kEpiBufBytes = epilogue_buf_bytes(kOut);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    // CTA pair: rank 0 issues the UMMAs for both, each CTA owns 128 rows of the 256-row tile
+    // and loads half of the B tile
+    const uint32_t cta_rank = kCtas == 2 ? cluster_cta_rank() : 0u;
     const uint32_t block_n = p.block_n;
+    const uint32_t load_n = block_n / kCtas;
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
     const SfPlan plan_a = sf_plan(p.gran_a, kBlockKElems), plan_b = sf_plan(p.gran_b, kBlockKElems);
     const uint32_t sfa_bytes = 512 * plan_a.words, sfb_bytes = sf_block_n * 4 * plan_b.words;
-    const uint32_t a_bytes = kBlockM * kBlockKBytes, b_bytes = block_n * kBlockKBytes;
+    const uint32_t a_bytes = kBlockM * kBlockKBytes, b_bytes = load_n * kBlockKBytes;
     const uint32_t num_stages = p.num_stages;
     const uint32_t num_k_blocks = (p.k + kBlockKElems - 1) / kBlockKElems;
 
@@ -164,13 +177,13 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem_a + num_stages * a_bytes;
     uint8_t* smem_epi = smem_b + num_stages * b_bytes;
-    uint8_t* smem_sfa = smem_epi + 8 * kEpilogueBufBytes;
+    uint8_t* smem_sfa = smem_epi + 8 * kEpiBufBytes;
     uint8_t* smem_sfb = smem_sfa + num_stages * sfa_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_sfb + num_stages * sfb_bytes);
-    uint64_t* bar_full = bars;
-    uint64_t* bar_empty = bars + kMaxStages;
-    uint64_t* bar_sf_raw = bars + 2 * kMaxStages;
-    uint64_t* bar_sf_ready = bars + 3 * kMaxStages;
+    uint64_t* bar_full = bars;                       // A/B tiles of a stage landed (pair: both CTAs' tiles, on rank 0)
+    uint64_t* bar_empty = bars + kMaxStages;         // the UMMAs reading a stage finished
+    uint64_t* bar_sf_raw = bars + 2 * kMaxStages;    // scale words of a stage landed (per CTA)
+    uint64_t* bar_sf_ready = bars + 3 * kMaxStages;  // scale words re-ordered (pair: both CTAs, on rank 0)
     uint64_t* bar_tmem_full = bars + 4 * kMaxStages;
     uint64_t* bar_tmem_empty = bars + 4 * kMaxStages + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kMaxStages + 4);
@@ -181,11 +194,11 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             mbar_init(bar_full + s, 1);
             mbar_init(bar_empty + s, 1);
             mbar_init(bar_sf_raw + s, 1);
-            mbar_init(bar_sf_ready + s, 1);
+            mbar_init(bar_sf_ready + s, kCtas);
         }
         for (uint32_t e = 0; e < 2; ++e) {
             mbar_init(bar_tmem_full + e, 1);
-            mbar_init(bar_tmem_empty + e, 4);
+            mbar_init(bar_tmem_empty + e, 4 * kCtas);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -196,97 +209,122 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         tma_prefetch_desc(&tmap_d);
     }
     if (warp == 1) {
-        tmem_alloc<1>(tmem_slot, kTmemCols);
-        tmem_relinquish<1>();
+        tmem_alloc<kCtas>(tmem_slot, kTmemCols);
+        tmem_relinquish<kCtas>();
     }
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kCtas == 2) cluster_sync(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_sfa = tmem_base + p.num_accum_stages * block_n;
     const uint32_t tmem_sfb = tmem_sfa + 4 * plan_a.words;
 
+    // The producer and UMMA warps run their loops with all 32 lanes and guard only the issuing
+    // instructions with lane 0: addresses and descriptors stay warp-uniform, so they live in
+    // uniform registers instead of being moved there one by one for every tcgen05 / TMA
+    // instruction (which alone costs ~190 cycles per UMMA).
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            Scheduler sched(p);
-            Tile t;
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            while (ok && sched.next(t)) {
-                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
-                    if (!mbar_wait(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
-                    const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+        Scheduler sched(p, kCtas);
+        Tile t;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        const uint32_t full_bar_leader = kCtas == 2 ? mapa_u32(smem_u32(bar_full), 0) : 0u;
+        while (ok && sched.next(t)) {
+            const int32_t row_a = static_cast<int32_t>(t.m0 + cta_rank * kBlockM);
+            const int32_t row_b = static_cast<int32_t>(t.n0 + cta_rank * load_n);
+            for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
+                const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                if (elect_one()) {
                     if (need_a || need_b) {
                         mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_bytes : 0u));
                         if (need_a)
-                            tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, static_cast<int32_t>(t.m0),
+                            tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, row_a,
                                         static_cast<int32_t>(t.ga * p.sf_a_cols + kb / plan_a.period * plan_a.words));
                         if (need_b)
                             tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0),
                                         static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words));
                     }
-                    mbar_arrive_expect_tx(bar_full + stage, a_bytes + b_bytes);
                     const int32_t kx = static_cast<int32_t>(kb * kBlockKElems);
-                    tma_load_3d(smem_a + stage * a_bytes, &tmap_a, bar_full + stage, kx, static_cast<int32_t>(t.m0),
-                                static_cast<int32_t>(t.ga));
-                    tma_load_3d(smem_b + stage * b_bytes, &tmap_b, bar_full + stage, kx, static_cast<int32_t>(t.n0),
-                                static_cast<int32_t>(t.gb));
-                    if (++stage == num_stages) { stage = 0; phase ^= 1; }
+                    if constexpr (kCtas == 1) {
+                        mbar_arrive_expect_tx(bar_full + stage, a_bytes + b_bytes);
+                        tma_load_3d(smem_a + stage * a_bytes, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
+                        tma_load_3d(smem_b + stage * b_bytes, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
+                    } else {
+                        // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
+                        if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * (a_bytes + b_bytes));
+                        const uint32_t bar_addr = full_bar_leader + stage * 8;
+                        tma_load_3d_2cta(smem_a + stage * a_bytes, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
+                        tma_load_3d_2cta(smem_b + stage * b_bytes, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
+                    }
                 }
+                if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------- UMMA issuer
-        if (lane == 0) {
-            Scheduler sched(p);
+        if (cta_rank == 0) {
+            Scheduler sched(p, kCtas);
             Tile t;
             uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0;
-            const uint32_t idesc = make_idesc_block_scaled(kBlockM, block_n, kMXF4 ? 1u : 0u, kMXF4 ? 1u : 0u);
+            const uint32_t idesc = make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : 0u, kMXF4 ? 1u : 0u);
+            const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
             while (ok && sched.next(t)) {
                 const uint32_t e = it % p.num_accum_stages, acc_phase = (it / p.num_accum_stages) & 1;
                 ++it;
-                if (!mbar_wait(bar_tmem_empty + e, acc_phase ^ 1, abort_flag, p.status, 0x200 + e)) break;
+                if (!mbar_wait_warp(bar_tmem_empty + e, acc_phase ^ 1, abort_flag, p.status, 0x200 + e)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + e * block_n;
                 for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
                     const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
-                    if (!mbar_wait(bar_full + stage, phase, abort_flag, p.status, 0x300 + stage)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar_full + stage, phase, abort_flag, p.status, 0x300 + stage)) { ok = false; break; }
                     if (need_a || need_b) {
-                        if (!mbar_wait(bar_sf_ready + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x400 + stage)) { ok = false; break; }
+                        if (!mbar_wait_warp(bar_sf_ready + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x400 + stage)) { ok = false; break; }
                         sf_phase_bits ^= 1u << stage;
                     }
                     tc_fence_after();
-                    if (need_a) {
-                        for (uint32_t c = 0; c < plan_a.words; ++c)
-                            utccp_32x128b_warpx4<1>(tmem_sfa + 4 * c, make_smem_desc(smem_u32(smem_sfa + stage * sfa_bytes + c * 512), 0, 128, 0));
-                    }
-                    if (need_b) {
-                        for (uint32_t c = 0; c < plan_b.words * (sf_block_n / 128); ++c)
-                            utccp_32x128b_warpx4<1>(tmem_sfb + 4 * c, make_smem_desc(smem_u32(smem_sfb + stage * sfb_bytes + c * 512), 0, 128, 0));
-                    }
+                    const uint32_t sfa_addr = smem_u32(smem_sfa + stage * sfa_bytes), sfb_addr = smem_u32(smem_sfb + stage * sfb_bytes);
                     const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes), 0, 1024, 2);
                     const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes), 0, 1024, 2);
+                    // everything the issuing lane needs is computed here, outside the single-lane region
+                    uint32_t idescs[4], a_cols[4], b_cols[4];
                     #pragma unroll
-                    for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
-                        uint32_t a_id, b_id, a_col, b_col;
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        uint32_t a_id, b_id;
                         if constexpr (kMXF4) {
                             // one UMMA spans 64 elements = two scale bytes; a word spans two UMMAs
                             a_id = (k & 1) * 2; b_id = (k & 1) * 2;
-                            a_col = 4 * (k / 2); b_col = 4 * (k / 2) * (sf_block_n / 128);
+                            a_cols[k] = tmem_sfa + 4 * (k / 2); b_cols[k] = tmem_sfb + 4 * (k / 2) * (sf_block_n / 128);
                         } else {
                             a_id = p.gran_a == 128 ? kb % 4 : k;
                             b_id = p.gran_b == 128 ? kb % 4 : k;
-                            a_col = 0; b_col = 0;
+                            a_cols[k] = tmem_sfa; b_cols[k] = tmem_sfb;
                         }
-                        umma_block_scaled<1, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4),
-                                                    idesc_with_sf_ids(idesc, a_id, b_id), tmem_sfa + a_col, tmem_sfb + b_col,
-                                                    (kb | k) != 0 ? 1u : 0u);
+                        idescs[k] = idesc_with_sf_ids(idesc, a_id, b_id);
                     }
-                    umma_commit(bar_empty + stage);
-                    if (kb + 1 == num_k_blocks) umma_commit(bar_tmem_full + e);
+                    const uint64_t sfa_desc = make_smem_desc(sfa_addr, 0, 128, 0), sfb_desc = make_smem_desc(sfb_addr, 0, 128, 0);
+                    const bool last = kb + 1 == num_k_blocks;
+                    if (elect_one()) {
+                        if (need_a)
+                            for (uint32_t c = 0; c < plan_a.words; ++c) utccp_32x128b_warpx4<kCtas>(tmem_sfa + 4 * c, sfa_desc + c * (512 >> 4));
+                        if (need_b)
+                            for (uint32_t c = 0; c < chunks_b; ++c) utccp_32x128b_warpx4<kCtas>(tmem_sfb + 4 * c, sfb_desc + c * (512 >> 4));
+                        #pragma unroll
+                        for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
+                            umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
+                                                            a_cols[k], b_cols[k], (kb | k) != 0 ? 1u : 0u);
+                        if constexpr (kCtas == 1) {
+                            umma_commit(bar_empty + stage);
+                            if (last) umma_commit(bar_tmem_full + e);
+                        } else {
+                            umma_commit_2cta(bar_empty + stage, 3);
+                            if (last) umma_commit_2cta(bar_tmem_full + e, 3);
+                        }
+                    }
+                    __syncwarp();
                     if (++stage == num_stages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -294,7 +332,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         __syncwarp();
     } else if (warp == 2) {
         // -------------------------------------------------- scale-factor re-ordering
-        Scheduler sched(p);
+        Scheduler sched(p, kCtas);
         Tile t;
         uint32_t stage = 0, sf_phase_bits = 0;
         bool ok = true;
@@ -316,7 +354,10 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_sf_ready + stage);
+                    if (lane == 0) {
+                        if constexpr (kCtas == 1) mbar_arrive(bar_sf_ready + stage);
+                        else mbar_arrive_remote(bar_sf_ready + stage, 0);
+                    }
                 }
                 if (++stage == num_stages) stage = 0;
             }
@@ -324,11 +365,15 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue
-        const uint32_t ew = warp - 4;  // TMEM lane quadrant and 32-row slice of the tile
-        uint8_t* buf0 = smem_epi + ew * 2 * kEpilogueBufBytes;
-        constexpr uint32_t kSubsPerBuf = kOut == kOutBf16 ? 2 : (kOut == kOutF32 ? 1 : 4);  // 32-column steps per 128-byte row
+        // 32 accumulator columns at a time: one tcgen05.ld per step; bf16 / f32 / e4m3 rows are staged
+        // in rows of kRowBytes (64 / 128 / 128 bytes, swizzled like the store's tensor map) and
+        // every kSubsPerBuf steps one TMA store writes 32 rows
+        const uint32_t ew = warp - 4;  // TMEM lane quadrant and 32-row slice of this CTA's 128 rows
+        uint8_t* buf0 = smem_epi + ew * 2 * kEpiBufBytes;
+        constexpr uint32_t kSubsPerBuf = kOut == kOutFp8 ? 4 : 1;
         constexpr uint32_t kColsPerBuf = 32 * kSubsPerBuf;
-        Scheduler sched(p);
+        constexpr uint32_t kRowBytes = kOut == kOutBf16 ? 64 : 128;
+        Scheduler sched(p, kCtas);
         Tile t;
         uint32_t it = 0, buf_idx = 0;
         while (sched.next(t)) {
@@ -337,7 +382,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             if (!mbar_wait(bar_tmem_full + e, acc_phase, abort_flag, p.status, 0x600 + e)) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((ew * 32) << 16) + e * block_n;
-            const uint32_t row = t.m0 + ew * 32 + lane;  // row this thread owns
+            const uint32_t row0 = t.m0 + cta_rank * kBlockM + ew * 32;
+            const uint32_t row = row0 + lane;  // row this thread owns
             const uint32_t num_subs = block_n / 32;
             uint32_t sf_word = 0;
             for (uint32_t s = 0; s < num_subs; ++s) {
@@ -348,10 +394,13 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     // the accumulator is in registers: hand the TMEM stage back to the UMMA warp
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_tmem_empty + e);
+                    if (lane == 0) {
+                        if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
+                        else mbar_arrive_remote(bar_tmem_empty + e, 0);
+                    }
                 }
                 const uint32_t sub_in_buf = s % kSubsPerBuf;
-                uint8_t* buf = buf0 + buf_idx * kEpilogueBufBytes;
+                uint8_t* buf = buf0 + buf_idx * kEpiBufBytes;
                 if (sub_in_buf == 0) {
                     // the store issued two buffers ago must have finished reading this buffer
                     if (lane == 0) tma_store_wait_read<1>();
@@ -361,11 +410,12 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     #pragma unroll
                     for (uint32_t i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.alpha);
                 }
-                const uint32_t row_addr = smem_u32(buf) + lane * 128;
+                const uint32_t row_addr = smem_u32(buf) + lane * kRowBytes;
                 if constexpr (kOut == kOutBf16) {
+                    // 64-byte rows, 64B swizzle: 16-byte chunk index ^ ((row / 2) % 4)
                     #pragma unroll
                     for (uint32_t j = 0; j < 4; ++j) {
-                        const uint32_t chunk = (sub_in_buf * 4 + j) ^ (lane & 7);
+                        const uint32_t chunk = j ^ ((lane >> 1) & 3);
                         st_shared_v4(row_addr + chunk * 16,
                                      pack_bf16x2(__uint_as_float(v[8 * j + 0]), __uint_as_float(v[8 * j + 1])),
                                      pack_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3])),
@@ -400,8 +450,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         uint32_t w[4];
                         #pragma unroll
                         for (uint32_t q = 0; q < 4; ++q)
-                            w[q] = cvt_e4m3x4(__uint_as_float(v[16 * j + 4 * q + 0]) * inv + 0.0f, __uint_as_float(v[16 * j + 4 * q + 1]) * inv + 0.0f,
-                                              __uint_as_float(v[16 * j + 4 * q + 2]) * inv + 0.0f, __uint_as_float(v[16 * j + 4 * q + 3]) * inv + 0.0f);
+                            w[q] = cvt_e4m3x4(scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 0]), inv), scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 1]), inv),
+                                              scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 2]), inv), scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 3]), inv));
                         st_shared_v4(row_addr + chunk * 16, w[0], w[1], w[2], w[3]);
                     }
                 }
@@ -415,8 +465,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (col0 < p.n && t.m0 + ew * 32 < p.m)
-                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(t.m0 + ew * 32), static_cast<int32_t>(t.ga));
+                        if (col0 < p.n && row0 < p.m)
+                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.ga));
                         tma_store_commit();
                     }
                     buf_idx ^= 1;
@@ -428,18 +478,18 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     }
 
     tc_fence_before();
-    __syncthreads();
+    if constexpr (kCtas == 2) cluster_sync(); else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc<1>(tmem_base, kTmemCols);
+        tmem_dealloc<kCtas>(tmem_base, kTmemCols);
     }
 }
 
 // Bytes of dynamic shared memory the kernel needs for a configuration (host side).
-inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t stages, uint32_t sfa_words, uint32_t sfb_words) {
+inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t ctas, uint32_t out_kind, uint32_t stages, uint32_t sfa_words, uint32_t sfb_words) {
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
-    const uint32_t per_stage = kBlockM * kBlockKBytes + block_n * kBlockKBytes + 512 * sfa_words + sf_block_n * 4 * sfb_words;
-    return 1024 + stages * per_stage + 8 * kEpilogueBufBytes + (4 * kMaxStages + 4) * 8 + 16;
+    const uint32_t per_stage = kBlockM * kBlockKBytes + block_n / ctas * kBlockKBytes + 512 * sfa_words + sf_block_n * 4 * sfb_words;
+    return 1024 + stages * per_stage + 8 * epilogue_buf_bytes(out_kind) + (4 * kMaxStages + 4) * 8 + 16;
 }
 
 }  // namespace dg

@@ -89,6 +89,14 @@ DG_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abor
     }
 }
 
+// Whole-warp flavour: every lane polls, the verdict is combined with a vote so the branch that
+// follows is warp-uniform (the compiler then keeps loop state, addresses and descriptors in
+// uniform registers, which the TMA and tcgen05 issue paths read directly).
+DG_DEVICE bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, Status* status, uint32_t site) {
+    const bool ok = mbar_wait(bar, parity, abort_flag, status, site);
+    return __all_sync(0xFFFFFFFFu, ok);
+}
+
 // -------------------------------------------------------------------- fences
 DG_DEVICE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 DG_DEVICE void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -304,6 +312,11 @@ DG_DEVICE uint32_t cvt_e2m1x8(const float* v) {
         : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
     return r;
 }
+// v * inv rounded to f32, with a product of -0.0 (exact or underflowed) turned into +0.0: the CPU
+// encoder takes the sign from (v < 0) after the multiply, the hardware conversion keeps the sign bit.
+// Separate rounded multiply and add on purpose: a fused multiply-add would keep the sign of an
+// underflowing product.
+DG_DEVICE float scale_pos_zero(float v, float inv) { return __fadd_rn(__fmul_rn(v, inv), 0.0f); }
 DG_DEVICE void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
