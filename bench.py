@@ -53,7 +53,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -208,22 +208,37 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    fence()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    fence()
     dominant_events = []
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     fence()
+    n_before = len(sampler.samples)
     start.record()
     for _ in range(args.steps):
         step(dominant_events)
     end.record()
     fence()
+    n_timed = len(sampler.samples) - n_before
     ms = start.elapsed_time(end)
+    # the timed region lasts milliseconds; keep the same step loop running for about a second so the
+    # clock record also shows what the GPU settles at under this load
+    if rank == 0:
+        t_soak = time.perf_counter()
+        while time.perf_counter() - t_soak < 1.2:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = "warm-up + timed region + 1.2 s of the same step loop"
+        clocks["samples_in_timed_region"] = n_timed
+    if world > 1:
+        dist.barrier()
     ctx.sync()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:

@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_HERE, "libdgb200.so")
+_LIB_PATH = os.environ.get("DGB200_LIBRARY") or os.path.join(_HERE, "libdgb200.so")  # override: an alternative build of the same ABI
 INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 
 

@@ -433,6 +433,14 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.sfd_stride = align4(pr.m);
     p.grouped_layout = pr.layout;
     p.status = ctx->status;
+#ifdef DG_PROFILE
+    {   // debug builds: DG_PROF_PTR carries a device buffer address (8 x int64 per CTA)
+        const char* pp = getenv("DG_PROF_PTR");
+        p.prof = pp ? reinterpret_cast<long long*>(strtoull(pp, nullptr, 0)) : nullptr;
+        const char* df = getenv("DG_DEBUG_FLAGS");
+        p.debug_flags = df ? static_cast<uint32_t>(atoi(df)) : 0;
+    }
+#endif
 
     const uint32_t ctas = cfg.cluster_m;
     uint32_t grid = static_cast<uint32_t>(ctx->num_sms) / ctas * ctas;

@@ -55,7 +55,19 @@ struct GemmParams {
     const uint32_t* grouped_layout;  // contiguous: end row of each group; masked: valid rows per group
     uint32_t* sfd;
     Status* status;
+    long long* prof;           // debug builds only
+    uint32_t debug_flags;      // debug builds only: 1 = epilogue only releases the accumulator, 2 = no scale-factor traffic
 };
+
+// Optional cycle accounting of the UMMA warp (debug builds with -DDG_PROFILE): p.prof[block*8 + i]
+// i = 0 loop total, 1 wait for tiles, 2 wait for scales, 3 issue, 4 wait for a free accumulator.
+#ifdef DG_PROFILE
+#define DG_PROF_T(var) const long long var = clock64()
+#define DG_PROF_ADD(slot, t0) prof_acc[slot] += clock64() - (t0)
+#else
+#define DG_PROF_T(var)
+#define DG_PROF_ADD(slot, t0)
+#endif
 
 struct Tile {
     uint32_t m0, n0;     // first row / column of the tile (row is group-local except in the contiguous arena)
@@ -235,7 +247,10 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             const int32_t row_b = static_cast<int32_t>(t.n0 + cta_rank * load_n);
             for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
                 if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
-                const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+#ifdef DG_PROFILE
+                if (p.debug_flags & 2) need_a = need_b = false;
+#endif
                 if (elect_one()) {
                     if (need_a || need_b) {
                         mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_bytes : 0u));
@@ -272,19 +287,33 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             const uint32_t idesc = make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : 0u, kMXF4 ? 1u : 0u);
             const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
+#ifdef DG_PROFILE
+            long long prof_acc[5] = {0, 0, 0, 0, 0};
+#endif
+            DG_PROF_T(t_loop);
             while (ok && sched.next(t)) {
                 const uint32_t e = it % p.num_accum_stages, acc_phase = (it / p.num_accum_stages) & 1;
                 ++it;
+                DG_PROF_T(t_acc);
                 if (!mbar_wait_warp(bar_tmem_empty + e, acc_phase ^ 1, abort_flag, p.status, 0x200 + e)) break;
+                DG_PROF_ADD(4, t_acc);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + e * block_n;
                 for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
-                    const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                    bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+#ifdef DG_PROFILE
+                    if (p.debug_flags & 2) need_a = need_b = false;
+#endif
+                    DG_PROF_T(t_full);
                     if (!mbar_wait_warp(bar_full + stage, phase, abort_flag, p.status, 0x300 + stage)) { ok = false; break; }
+                    DG_PROF_ADD(1, t_full);
+                    DG_PROF_T(t_sf);
                     if (need_a || need_b) {
                         if (!mbar_wait_warp(bar_sf_ready + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x400 + stage)) { ok = false; break; }
                         sf_phase_bits ^= 1u << stage;
                     }
+                    DG_PROF_ADD(2, t_sf);
+                    DG_PROF_T(t_issue);
                     tc_fence_after();
                     const uint32_t sfa_addr = smem_u32(smem_sfa + stage * sfa_bytes), sfb_addr = smem_u32(smem_sfb + stage * sfb_bytes);
                     const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes), 0, 1024, 2);
@@ -325,9 +354,15 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         }
                     }
                     __syncwarp();
+                    DG_PROF_ADD(3, t_issue);
                     if (++stage == num_stages) { stage = 0; phase ^= 1; }
                 }
             }
+#ifdef DG_PROFILE
+            DG_PROF_ADD(0, t_loop);
+            if (lane == 0 && p.prof != nullptr)
+                for (int i = 0; i < 5; ++i) p.prof[blockIdx.x * 8 + i] = prof_acc[i];
+#endif
         }
         __syncwarp();
     } else if (warp == 2) {
@@ -338,7 +373,10 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         bool ok = true;
         while (ok && sched.next(t)) {
             for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
-                const bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+#ifdef DG_PROFILE
+                if (p.debug_flags & 2) need_a = need_b = false;
+#endif
                 if (need_a || need_b) {
                     if (!mbar_wait(bar_sf_raw + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x500 + stage)) { ok = false; break; }
                     sf_phase_bits ^= 1u << stage;
@@ -386,6 +424,17 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             const uint32_t row = row0 + lane;  // row this thread owns
             const uint32_t num_subs = block_n / 32;
             uint32_t sf_word = 0;
+#ifdef DG_PROFILE
+            if (p.debug_flags & 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
+                    else mbar_arrive_remote(bar_tmem_empty + e, 0);
+                }
+                continue;
+            }
+#endif
             for (uint32_t s = 0; s < num_subs; ++s) {
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(taddr + s * 32, v);

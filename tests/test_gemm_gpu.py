@@ -76,6 +76,22 @@ def test_dense_fp8_small(ctx, m, n, k):
     run_dense(ctx, m, n, k)
 
 
+@pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("block_n", [32, 64, 96, 128, 160, 192, 224, 256])
+def test_dense_fp8_every_tile_shape(ctx, ctas, block_n, monkeypatch):
+    # DG_BLOCK_N / DG_CTAS pin the tile the heuristic would otherwise choose: every width the epilogue can
+    # store, single CTA and CTA pair (256-row tiles, B split between the two CTAs), single- and
+    # double-buffered accumulators, with ragged M and N so edge tiles are partly out of bounds
+    if block_n % (16 * ctas) != 0:
+        pytest.skip("tile width not issuable")
+    monkeypatch.setenv("DG_BLOCK_N", str(block_n))
+    monkeypatch.setenv("DG_CTAS", str(ctas))
+    cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 600, 1000, 1152))
+    assert cfg.block_n == block_n and cfg.cluster_m == ctas and cfg.block_m == 128 * ctas
+    run_dense(ctx, 600, 1000, 1152, seed=block_n + ctas)
+    run_dense(ctx, 600, 1000, 1152, out_kind=1, seed=block_n + ctas)
+
+
 def test_dense_fp8_matches_scalar_reference_and_golden(ctx):
     # the committed fixture holds quantised inputs of the 128x256x512 case and the output of the scalar
     # restatement of ref_fp8_gemm_nt (f32); the GPU f32 output must agree with it
