@@ -1,6 +1,6 @@
 """Ahead-of-time build of libdgb200.so (the C-ABI library) with nvcc for sm_100a.
 
-`python -m deepgemm_rust_b200.build` (or build()) compiles csrc/dg_api.cu, which includes the
+`python deepgemm_rust_b200/build.py` (or build()) compiles csrc/dg_api.cu, which includes the
 kernel headers, into deepgemm_rust_b200/libdgb200.so.  nvcc cross-compiles without a GPU.
 """
 import os

@@ -56,7 +56,7 @@ def test_heuristics_block_k_and_budgets():
     d8 = dg.Sm100Desc(dg.GemmType.Normal, 4096, 7168, 7168)
     c8 = dg.best_config(d8)
     assert c8.block_k == 128 and c8.num_stages >= 2 and c8.smem_size <= dg.SM100_SMEM_CAPACITY
-    assert c8.block_m == 128 and c8.block_n % 16 == 0 and c8.block_n <= 256
+    assert c8.block_m == 128 * c8.cluster_m and c8.cluster_m in (1, 2) and c8.block_n % 16 == 0 and c8.block_n <= 256
     # TMEM budget: accumulators (x stages) plus scale columns within 512 columns
     for c, sf_cols in ((c8, 4 + 4 * ((c8.block_n + 127) // 128)), (c4, 8 + 8 * ((c4.block_n + 127) // 128))):
         assert c.num_accum_stages * c.block_n + sf_cols <= 512
@@ -66,7 +66,14 @@ def test_heuristics_grouped_and_output_kinds():
     # tests/unit.rs:43-70: the m-grouped layouts tile M by the 128-row alignment
     d = dg.Sm100Desc(dg.GemmType.MGroupedContiguous, 8192, 7168, 7168, num_groups=256)
     c = dg.best_config(d)
-    assert c.block_m == 128 and c.smem_size <= dg.SM100_SMEM_CAPACITY
+    assert c.block_m == 128 and c.cluster_m == 1 and c.smem_size <= dg.SM100_SMEM_CAPACITY
+    # tests/unit.rs:160-195: with the 256-row alignment the tile may follow the knob (a CTA pair per 256 rows)
+    dg.set_mk_alignment_for_contiguous_layout(256)
+    try:
+        c = dg.best_config(d)
+        assert c.block_m in (128, 256) and c.block_m == 128 * c.cluster_m and c.smem_size <= dg.SM100_SMEM_CAPACITY
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
     # FP8 output stores 128-column rows, so BLOCK_N is a multiple of 128
     c = dg.best_config(dg.Sm100Desc(dg.GemmType.MGroupedMasked, 256, 4096, 7168, num_groups=32, expected_m=128, cd_dtype=2))
     assert c.block_n % 128 == 0
