@@ -32,7 +32,7 @@ class DgError(RuntimeError):
 def _load():
     if not os.path.exists(_LIB_PATH):
         raise ImportError(
-            f"{_LIB_PATH} is missing: build it with `python -m deepgemm_rust_b200.build` "
+            f"{_LIB_PATH} is missing: build it with `python deepgemm_rust_b200/build.py` "
             "(nvcc, sm_100a). There is no fallback implementation.")
     return C.CDLL(_LIB_PATH)
 
@@ -87,6 +87,8 @@ _gemm_contig = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous", C.c_int, _vp, C.PO
                       C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
 _gemm_contig_ends = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_ends", C.c_int, _vp, C.POINTER(_LpOperand), _vp,
                            C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_gemm_contig_static = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_static", C.c_int, C.c_int, _vp, C.POINTER(_LpOperand), _vp,
+                             C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
 _gemm_masked = _proto("dg_m_grouped_fp8_fp4_gemm_masked", C.c_int, _vp, C.POINTER(_LpOperand), _vp, C.POINTER(_LpOperand),
                       C.POINTER(_Out), _u32, _u32, C.POINTER(_Epilogue))
 _bmm = _proto("dg_fp8_fp4_bmm", C.c_int, _vp, C.POINTER(_LpOperand), C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
@@ -245,6 +247,21 @@ def m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a, group_ends: torch.Tensor,
     """Same GEMM from a prebuilt group-end table (see psum_from_m_indices_dev)."""
     ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
     _check(_gemm_contig_ends(ctx._h, C.byref(ca), _vp(group_ends.data_ptr()), C.byref(cb), C.byref(co), num_groups, C.byref(ce)))
+
+
+STATIC_MAX_GROUPS = 4096
+
+
+def m_grouped_fp8_fp4_gemm_contiguous_static_dev(device: int, cuda_stream: int, a, m_indices: torch.Tensor, b, out, num_groups: int,
+                                                 epi=None):
+    """The contiguous grouped GEMM without a context and without any allocation (no reference
+    counterpart): for hosts that may not call the device allocator while running.  Its scratch is an
+    array inside the library, shared by all calls on a device (keep them on one stream), good for up
+    to STATIC_MAX_GROUPS groups.  The first call on a device does a one-time address lookup and
+    should come before any stream capture."""
+    ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
+    _check(_gemm_contig_static(device, _vp(cuda_stream), C.byref(ca), _vp(m_indices.data_ptr()), C.byref(cb), C.byref(co), num_groups,
+                               C.byref(ce)))
 
 
 def m_grouped_fp8_fp4_gemm_masked_dev(ctx, a, masked_m: torch.Tensor, b, out, num_groups: int, expected_m: int, epi=None):

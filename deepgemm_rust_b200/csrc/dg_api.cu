@@ -522,6 +522,70 @@ int dg_fp8_fp4_bmm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, 
     return launch_gemm(ctx, a, b, out, epi, pr);
 }
 
+// ------------------------------------------------------- entry point that allocates nothing
+// Scratch for dg_m_grouped_fp8_fp4_gemm_contiguous_static: words [0, 4) are the record a kernel
+// writes when one of its bounded waits runs out, words [64, 64 + kStaticMaxGroups) hold the
+// group-end table.  One copy per GPU that loads the library, kept until the process exits.
+constexpr uint32_t kStaticMaxGroups = DG_STATIC_MAX_GROUPS;
+constexpr uint32_t kStaticEndsOffset = 64;
+static __device__ __align__(256) uint32_t g_static_scratch[kStaticEndsOffset + kStaticMaxGroups];
+
+namespace {
+struct StaticDevice {
+    bool ready = false;
+    uint32_t* scratch = nullptr;   // device address of g_static_scratch on this device
+    int num_sms = 0;
+};
+StaticDevice g_static_devices[64];
+std::mutex g_static_mutex;
+
+// Once per device, with that device current: ask the runtime for the device address of the array.
+// In host code the array's name is only a handle for this lookup, never a pointer a kernel can use.
+int static_device_setup(int device, StaticDevice** out) {
+    if (device < 0 || device >= 64) return fail(DG_ERR_SHAPE, "device ordinal %d out of range", device);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticDevice& d = g_static_devices[device];
+    if (!d.ready) {
+        DG_CUDA(cudaSetDevice(device));
+        int major = 0;
+        DG_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+        if (major != 10) return fail(DG_ERR_UNSUPPORTED, "device %d is not sm_100; these kernels are built for sm_100a only", device);
+        if (encode_tiled_fn() == nullptr) return fail(DG_ERR_DRIVER, "cuTensorMapEncodeTiled not found in the driver");
+        DG_CUDA(cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, device));
+        uint32_t* ptr = nullptr;
+        DG_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
+        d.scratch = ptr;
+        d.ready = true;
+    }
+    *out = &d;
+    return DG_OK;
+}
+}  // namespace
+
+int dg_m_grouped_fp8_fp4_gemm_contiguous_static(int device, void* cuda_stream, const dg_lp_operand* a, const int32_t* m_indices,
+                                                const dg_lp_operand* b, const dg_out* out, uint32_t num_groups, const dg_epilogue* epi) {
+    if (!a || !b || !out || !m_indices) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_groups == 0) return fail(DG_ERR_SHAPE, "num_groups must be positive");
+    if (num_groups > kStaticMaxGroups)
+        return fail(DG_ERR_SHAPE, "num_groups (%u) exceeds the %u groups the built-in scratch holds; use dg_m_grouped_fp8_fp4_gemm_contiguous",
+                    num_groups, kStaticMaxGroups);
+    StaticDevice* dev = nullptr;
+    int rc = static_device_setup(device, &dev);
+    if (rc) return rc;
+    DG_CUDA(cudaSetDevice(device));
+    // a context view on the stack: nothing is created, nothing has to be destroyed
+    dg_ctx view;
+    view.ordinal = device;
+    view.stream = static_cast<cudaStream_t>(cuda_stream);
+    view.num_sms = dev->num_sms;
+    view.status = reinterpret_cast<dg::Status*>(dev->scratch);
+    uint32_t* ends = dev->scratch + kStaticEndsOffset;
+    // the table keeps the previous call's contents: run_group_ends clears the entries it is about to fill
+    rc = run_group_ends(&view, m_indices, a->rows, num_groups, ends);
+    if (rc) return rc;
+    return dg_m_grouped_fp8_fp4_gemm_contiguous_ends(&view, a, ends, b, out, num_groups, epi);
+}
+
 // ------------------------------------------------------------------ quantise / re-layout
 static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran, uint32_t groups, int rule,
                        bool fp4, uint8_t* dst, uint32_t* sf) {

@@ -93,6 +93,26 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous(dg_ctx* ctx, const dg_lp_operand* a, co
 int dg_m_grouped_fp8_fp4_gemm_contiguous_ends(dg_ctx* ctx, const dg_lp_operand* a, const uint32_t* group_ends, const dg_lp_operand* b,
                                               const dg_out* out, uint32_t num_groups, const dg_epilogue* epi);
 
+/* No counterpart in the reference.  The contiguous grouped GEMM for hosts that must not touch the
+ * device allocator once they are running -- for instance a serving process that handed every byte of
+ * device memory to its own pool at start-up (so a cudaMalloc can only fail), or a latency-critical
+ * loop where the implicit device-wide synchronisation of cudaMalloc / cudaFree would stall every
+ * stream.  It needs no dg_ctx and allocates nothing, neither on the device nor through any
+ * allocating library routine: the group-end table it builds from m_indices, and the record its
+ * kernels write if a bounded wait runs out, live in an array that is part of the library image
+ * (about 16.3 KB on every GPU that loads the library, held until the process exits).
+ *   - num_groups may be at most DG_STATIC_MAX_GROUPS; larger values return DG_ERR_SHAPE.
+ *   - The first call on a device looks up the array's device address (once, with that device
+ *     current).  Make that first call before any stream capture.
+ *   - Every call on a device uses the same array, which still holds the previous call's table; the
+ *     call clears the entries it needs on `cuda_stream` first.  Two calls whose GPU work can overlap
+ *     (different streams, or different threads) race on it: keep them on one stream.
+ *   - Arguments and results are those of dg_m_grouped_fp8_fp4_gemm_contiguous; `cuda_stream` is the
+ *     cudaStream_t to enqueue on. */
+#define DG_STATIC_MAX_GROUPS 4096
+int dg_m_grouped_fp8_fp4_gemm_contiguous_static(int device, void* cuda_stream, const dg_lp_operand* a, const int32_t* m_indices,
+                                                const dg_lp_operand* b, const dg_out* out, uint32_t num_groups, const dg_epilogue* epi);
+
 /* ops_sm100.rs:815 (m_grouped_fp8_fp4_gemm_masked_dev).  a.rows = m_max (per group), data
  * (num_groups, m_max, k); b.rows = num_groups * n; masked_m (device, int32 per group) is read on
  * the device.  Unlike the reference, DG_OUT_FP8 is accepted here: D is (num_groups, m_max, n)
