@@ -3,9 +3,15 @@
     python bench.py --gpus N --steps K --warmup W [--workload dense_fp8] [--impl reference]
 
 Workloads (all synthetic: seeded N(0,1) bf16 matrices quantised to e4m3 with per-128 UE8M0 scales):
-  dense_fp8   one step = one pass over the ten dense DeepSeek-V3 projection GEMMs
+  dense_fp8   (default at N = 1) one step = one pass over the ten dense DeepSeek-V3 projection GEMMs
               M in {128, 4096} x (N, K) in {(2112,7168), (24576,1536), (7168,16384), (4096,7168), (7168,2048)}.
-              With N > 1 GPUs every rank runs its own replica (the dense GEMM does not shard).
+              The dense GEMM does not shard; with --workload dense_fp8 at N > 1 every rank runs a replica.
+  moe_ep      (default at N > 1) the contiguous m-grouped FP8 GEMM pair of a DeepSeek-V3 MoE layer, experts
+              sharded 256/N per GPU: 8192 tokens per rank, top-8 of 256 experts from softmax of seeded N(0,1)
+              router logits; one step = plan + all-to-all dispatch of e4m3 rows and scales + gate/up grouped
+              GEMM (N=4096, K=7168) + down grouped GEMM (N=7168, K=2048, on an independent resident operand:
+              the benchmark defines the two GEMMs as independent) + all-to-all combine and weighted
+              reduction.  Flops count the routed (unpadded) rows of both GEMMs.
 The metric is whole-job TFLOP/s: 2*M*N*K summed over the GEMMs of a step, times ranks, over the
 step time (CUDA events, max over ranks).  `e2e` is the same pass driven from pinned host buffers
 (operands copied host->device and the result device->host inside the timed region).
@@ -142,13 +148,179 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+MOE = {"experts": 256, "topk": 8, "tokens_per_rank": 8192, "hidden": 7168, "gate_up_n": 4096, "down_k": 2048, "down_n": 7168}
+
+
+def run_moe(args, torch, dist, dg, rank, world, local_rank):
+    """Expert-parallel contiguous grouped GEMM workload (see the module docstring)."""
+    from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel
+    c = MOE
+    dev = torch.device("cuda", local_rank)
+    ctx = dg.DgContext(local_rank)
+    peaks = measured_peaks()
+    local_e = c["experts"] // world
+    gen = torch.Generator(device=dev).manual_seed(3000 + rank)
+
+    def quant_weights(n, k):
+        q = torch.empty((local_e * n, k), dtype=torch.uint8, device=dev)
+        sf = dg.alloc_sf(ctx, local_e * n, k, 128, local_e)
+        cols, stride, chunk = dg.sf_packed_cols(k, 128), dg.sf_aligned_rows(n), 8
+        for g0 in range(0, local_e, chunk):
+            gn = min(chunk, local_e - g0)
+            w = torch.randn((gn * n, k), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+            wq, wsf = dg.cast_bf16_to_fp8_sf_dev(ctx, w, k, gn * n, k, 128, gn)
+            q[g0 * n:(g0 + gn) * n] = wq
+            sf.view(local_e, cols, stride)[g0:g0 + gn] = wsf.view(gn, cols, stride)
+        return q, sf
+
+    w1q, w1sf = quant_weights(c["gate_up_n"], c["hidden"])
+    w2q, w2sf = quant_weights(c["down_n"], c["down_k"])
+    tokens = c["tokens_per_rank"]
+    x = torch.randn((tokens, c["hidden"]), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    logits = torch.randn((tokens, c["experts"]), generator=gen, device=dev, dtype=torch.float32)
+    topw, topi = torch.softmax(logits, -1).topk(c["topk"], dim=-1)
+    topw = topw.contiguous()
+    xq, xsf = dg.cast_bf16_to_fp8_sf_dev(ctx, x, c["hidden"], tokens, c["hidden"], 128)
+    ep = ExpertParallel(c["experts"], c["topk"], DeviceRowOps(ctx))
+    cap = 2 * tokens * c["topk"] + 128 * local_e            # arena capacity for the resident down-GEMM operand
+    act = torch.randn((cap, c["down_k"]), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    actq, actsf_full = dg.cast_bf16_to_fp8_sf_dev(ctx, act, c["down_k"], cap, c["down_k"], 128)
+    del act
+    w1 = dg.LpOperand(w1q, w1sf, local_e * c["gate_up_n"], c["hidden"], c["hidden"])
+    w2 = dg.LpOperand(w2q, w2sf, local_e * c["down_n"], c["down_k"], c["down_k"])
+    ctx.sync()
+    stats = {}
+
+    def step(xq_, xsf_, topi_, topw_):
+        plan = ep.plan(topi_)
+        if plan.m_pad > cap:
+            raise RuntimeError(f"arena of {plan.m_pad} rows exceeds the benchmark capacity {cap}")
+        a, a_sf = ep.dispatch(plan, xq_, xsf_, c["hidden"])
+        h = torch.empty((plan.m_pad, c["gate_up_n"]), dtype=torch.bfloat16, device=dev)
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(a, a_sf, plan.m_pad, c["hidden"], c["hidden"]), plan.m_indices, w1,
+                                                 dg.Sm100Out.Bf16(h, c["gate_up_n"]), local_e)
+        # the resident operand's scale words use stride align4(cap); the GEMM wants stride align4(m_pad): rows are a prefix,
+        # so pass the full-capacity view (rows = cap) and let the group table bound the work
+        y = torch.empty((cap, c["down_n"]), dtype=torch.bfloat16, device=dev)
+        m_idx_cap = torch.full((cap,), -1, dtype=torch.int32, device=dev)
+        m_idx_cap[:plan.m_pad] = plan.m_indices
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(actq, actsf_full, cap, c["down_k"], c["down_k"]), m_idx_cap, w2,
+                                                 dg.Sm100Out.Bf16(y, c["down_n"]), local_e)
+        out = ep.combine(plan, y, topw_)
+        stats["rows"] = plan.n_recv
+        stats["m_pad"] = plan.m_pad
+        return out
+
+    def fence():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step(xq, xsf, topi, topw)
+    fence()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step(xq, xsf, topi, topw)
+    end.record()
+    fence()
+    t = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
+    rows = torch.tensor([float(stats["rows"])], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rows, op=dist.ReduceOp.SUM)
+    ms_per_step = float(t.item()) / args.steps
+    flops_per_row = 2.0 * (c["gate_up_n"] * c["hidden"] + c["down_n"] * c["down_k"])
+    value = float(rows.item()) * flops_per_row / (ms_per_step * 1e-3) / 1e12
+
+    # the gate/up grouped GEMM alone (dominant kernel of this workload), CUDA events on its stream
+    plan = ep.plan(topi)
+    a, a_sf = ep.dispatch(plan, xq, xsf, c["hidden"])
+    h = torch.empty((plan.m_pad, c["gate_up_n"]), dtype=torch.bfloat16, device=dev)
+    a_op = dg.LpOperand(a, a_sf, plan.m_pad, c["hidden"], c["hidden"])
+    times = []
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a_op, plan.m_indices, w1, dg.Sm100Out.Bf16(h, c["gate_up_n"]), local_e)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    gemm_ms = statistics.median(times[1:])
+    fence()
+
+    # end to end from pinned host buffers: this rank's quantised tokens, scales, routing in; reduced rows out
+    e2e = None
+    if not args.no_e2e:
+        hx, hsf, hi, hw = xq.cpu().pin_memory(), xsf.cpu().pin_memory(), topi.cpu().pin_memory(), topw.cpu().pin_memory()
+        hout = torch.empty((tokens, c["down_n"]), dtype=torch.bfloat16).pin_memory()
+        dx, dsf, di, dw = torch.empty_like(xq), torch.empty_like(xsf), torch.empty_like(topi), torch.empty_like(topw)
+
+        def e2e_step():
+            dx.copy_(hx, non_blocking=True)
+            dsf.copy_(hsf, non_blocking=True)
+            di.copy_(hi, non_blocking=True)
+            dw.copy_(hw, non_blocking=True)
+            hout.copy_(step(dx, dsf, di, dw), non_blocking=True)
+
+        e2e_steps = max(3, min(args.steps, 10))
+        e2e_step()
+        fence()
+        start.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        end.record()
+        fence()
+        t = torch.tensor([start.elapsed_time(end)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item()) / e2e_steps
+        h2d = sum(z.numel() * z.element_size() for z in (hx, hsf, hi, hw))
+        e2e = {"value": float(rows.item()) * flops_per_row / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": hout.numel() * hout.element_size(), "ms_per_step": e2e_ms, "steps": e2e_steps}
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.sync()
+    if rank == 0:
+        n_valid = plan.n_recv
+        gemm_flops = 2.0 * n_valid * c["gate_up_n"] * c["hidden"]
+        gemm_bytes = n_valid * c["hidden"] + local_e * c["gate_up_n"] * c["hidden"] + n_valid * c["gate_up_n"] * 2
+        t_tensor = gemm_flops / (2 * peaks["bf16_tflops_sustained"] * 1e12)
+        t_hbm = gemm_bytes / (peaks["hbm_gbs"] * 1e9)
+        if t_hbm > t_tensor:
+            roofline = {"bound": "hbm", "achieved": gemm_bytes / (gemm_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s"}
+        else:
+            roofline = {"bound": "tensor", "achieved": gemm_flops / (gemm_ms * 1e-3) / 1e12, "peak": 2 * peaks["bf16_tflops_sustained"],
+                        "unit": "TFLOP/s"}
+        roofline.update({"frac": roofline["achieved"] / roofline["peak"], "traffic": None,
+                         "kernel": "dg_gemm_kernel<fp8, bf16 out> contiguous grouped, gate/up",
+                         "launch": f"rank 0: {n_valid} routed rows over {local_e} local experts, N={c['gate_up_n']} K={c['hidden']}",
+                         "peak_source": f"{peaks['source']} peaks (tensor: 2 x bf16 sustained)", "us": gemm_ms * 1e3})
+        line = {"metric": "fp8_block_scaled_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "fp8_e4m3", "data": "synthetic",
+                "config": {"workload": "moe_contiguous_ep", **c, "experts_per_gpu": local_e, "mk_alignment": 128,
+                           "parallelism": f"ep{world}", "collective": "nccl all_to_all_single" if world > 1 else "none",
+                           "l2": "weights of one rank (0.9-7.5 GB) and the arena exceed the 126 MB L2"},
+                "clocks": clocks, "gpu_launches": args.steps * 10, "roofline": roofline}
+        if e2e is not None:
+            line["e2e"] = e2e
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="dgb200")
-    ap.add_argument("--workload", default="dense_fp8")
+    ap.add_argument("--workload", default=None, help="dense_fp8 (default at 1 GPU) or moe_ep (default at more)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--only", default=None, help="M,N,K: restrict the dense pass to one GEMM (profiling captures)")
@@ -172,6 +344,10 @@ def main():
     torch.cuda.set_device(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    workload = args.workload or ("dense_fp8" if world == 1 else "moe_ep")
+    if workload == "moe_ep":
+        run_moe(args, torch, dist, dg, rank, world, local_rank)
+        return
     dev = torch.device("cuda", local_rank)
     ctx = dg.DgContext(local_rank)
     peaks = measured_peaks()

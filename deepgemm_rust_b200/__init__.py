@@ -103,6 +103,10 @@ _tsf2d = _proto("dg_transform_sf2d_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32,
 _tsft = _proto("dg_transform_sf_t_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _vp)
 _group_ends = _proto("dg_group_ends_from_m_indices", C.c_int, _vp, _vp, _u32, _u32, _vp)
 _unpack_fp4 = _proto("dg_unpack_fp4_raw", C.c_int, _vp, _vp, _sz, _vp)
+_gather_rows = _proto("dg_gather_rows", C.c_int, _vp, _vp, _sz, _vp, _u32, _u32, _vp, _sz)
+_moe_pack = _proto("dg_moe_pack_rows", C.c_int, _vp, _vp, _u32, _vp, _u32, _u32, _vp, _u32, _vp, _sz)
+_moe_unpack = _proto("dg_moe_unpack_rows", C.c_int, _vp, _vp, _sz, _u32, _u32, _vp, _u32, _vp, _vp, _u32)
+_moe_combine = _proto("dg_moe_combine", C.c_int, _vp, _vp, _sz, _vp, _vp, _u32, _u32, _u32, _vp, _sz)
 _set_mk = _proto("dg_set_mk_alignment_for_contiguous_layout", C.c_int, _u32)
 _get_mk = _proto("dg_get_mk_alignment_for_contiguous_layout", _u32)
 _get_mk_theory = _proto("dg_get_theoretical_mk_alignment_for_contiguous_layout", _u32, _u32)
@@ -349,6 +353,45 @@ def unpack_fp4_raw_dev(ctx, src: torch.Tensor, packed_len: int) -> torch.Tensor:
     dst = torch.empty(packed_len * 2, dtype=torch.uint8, device=src.device)
     _check(_unpack_fp4(ctx._h, _vp(src.data_ptr()), packed_len, _vp(dst.data_ptr())))
     return dst
+
+
+def gather_rows_dev(ctx, src: torch.Tensor, idx: torch.Tensor, n_dst: int, dst: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dst row i = src row idx[i] for 2-D byte-addressable tensors (cuda/layout.rs:174 generalised); idx < 0 gives a zero row."""
+    row_bytes = src.shape[1] * src.element_size()
+    if dst is None:
+        dst = torch.empty((n_dst, src.shape[1]), dtype=src.dtype, device=src.device)
+    _check(_gather_rows(ctx._h, _vp(src.data_ptr()), src.stride(0) * src.element_size(), _vp(idx.data_ptr()), n_dst, row_bytes,
+                        _vp(dst.data_ptr()), dst.stride(0) * dst.element_size()))
+    return dst
+
+
+def moe_pack_rows_dev(ctx, data: torch.Tensor, sf: torch.Tensor, rows: int, k: int, gran_k: int, idx: torch.Tensor, pitch: int) -> torch.Tensor:
+    """All-to-all send rows: [k bytes of token idx[i] | its packed scale words | zero padding], `pitch` bytes each."""
+    n = idx.numel()
+    out = torch.empty((n, pitch), dtype=torch.uint8, device=data.device)
+    _check(_moe_pack(ctx._h, _vp(data.data_ptr()), k, _vp(sf.data_ptr()), sf_aligned_rows(rows), sf_packed_cols(k, gran_k), _vp(idx.data_ptr()), n,
+                     _vp(out.data_ptr()), pitch))
+    return out
+
+
+def moe_unpack_rows_dev(ctx, recv: torch.Tensor, k: int, gran_k: int, idx: torch.Tensor, n_dst: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Received rows -> (arena data (n_dst, k), packed scale words) with arena row i = received row idx[i] (-1: zero padding row)."""
+    data = torch.empty((n_dst, k), dtype=torch.uint8, device=recv.device)
+    cols, stride = sf_packed_cols(k, gran_k), sf_aligned_rows(n_dst)
+    sf = torch.zeros(cols * stride, dtype=torch.int32, device=recv.device)
+    _check(_moe_unpack(ctx._h, _vp(recv.data_ptr()), recv.stride(0), k, cols, _vp(idx.data_ptr()), n_dst, _vp(data.data_ptr()), _vp(sf.data_ptr()),
+                       stride))
+    return data, sf
+
+
+def moe_combine_dev(ctx, rows: torch.Tensor, pos: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """out[t] = bf16(sum_j weights[t, j] * rows[pos[t, j]]) (cuda/layout.rs:192-216 as a gather-reduce)."""
+    tokens, topk = pos.shape
+    n = rows.shape[1]
+    out = torch.empty((tokens, n), dtype=torch.bfloat16, device=rows.device)
+    _check(_moe_combine(ctx._h, _vp(rows.data_ptr()), rows.stride(0), _vp(pos.data_ptr()), _vp(weights.data_ptr()), tokens, topk, n,
+                        _vp(out.data_ptr()), out.stride(0)))
+    return out
 
 
 def set_mk_alignment_for_contiguous_layout(value: int):

@@ -15,6 +15,7 @@
 #include "../../include/dgb200.h"
 #include "dg_cast_kernels.cuh"
 #include "dg_gemm_kernel.cuh"
+#include "dg_moe_kernels.cuh"
 
 namespace {
 
@@ -687,6 +688,60 @@ int dg_unpack_fp4_raw(dg_ctx* ctx, const uint8_t* src, size_t packed_len, uint8_
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     const uint64_t threads = (packed_len + 15) / 16;
     dg::dg_unpack_fp4_kernel<<<static_cast<uint32_t>((threads + 255) / 256), 256, 0, ctx->stream>>>(src, dst, packed_len);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+// ------------------------------------------------------------------ MoE row movers
+static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+int dg_gather_rows(dg_ctx* ctx, const void* src, size_t src_pitch, const int32_t* idx, uint32_t n_dst, uint32_t row_bytes, void* dst,
+                   size_t dst_pitch) {
+    if (!ctx || !src || !idx || !dst) return fail(DG_ERR_SHAPE, "null argument");
+    if (row_bytes % 16 || src_pitch % 16 || dst_pitch % 16 || !aligned16(src) || !aligned16(dst))
+        return fail(DG_ERR_SHAPE, "rows, pitches and base addresses must be multiples of 16 bytes");
+    if (n_dst == 0) return DG_OK;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_gather_rows_kernel<<<ceil_div(n_dst, 8), 256, 0, ctx->stream>>>(static_cast<const uint8_t*>(src), src_pitch, idx, n_dst, row_bytes,
+                                                                           static_cast<uint8_t*>(dst), dst_pitch);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_moe_pack_rows(dg_ctx* ctx, const uint8_t* data, uint32_t k, const uint32_t* sf, uint32_t sf_stride, uint32_t sf_cols, const int32_t* idx,
+                     uint32_t n, uint8_t* out, size_t out_pitch) {
+    if (!ctx || !data || !sf || !idx || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (k % 16 || out_pitch % 16 || out_pitch < static_cast<size_t>(k) + 4 * sf_cols || !aligned16(data) || !aligned16(out))
+        return fail(DG_ERR_SHAPE, "k and out_pitch must be multiples of 16 and out_pitch >= k + 4 * sf_cols");
+    if (n == 0) return DG_OK;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_moe_pack_rows_kernel<<<ceil_div(n, 8), 256, 0, ctx->stream>>>(data, k, sf, sf_stride, sf_cols, idx, n, out, out_pitch);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_moe_unpack_rows(dg_ctx* ctx, const uint8_t* in, size_t in_pitch, uint32_t k, uint32_t sf_cols, const int32_t* idx, uint32_t n_dst,
+                       uint8_t* dst_data, uint32_t* dst_sf, uint32_t dst_sf_stride) {
+    if (!ctx || !in || !idx || !dst_data || !dst_sf) return fail(DG_ERR_SHAPE, "null argument");
+    if (k % 16 || in_pitch % 16 || in_pitch < static_cast<size_t>(k) + 4 * sf_cols || !aligned16(in) || !aligned16(dst_data))
+        return fail(DG_ERR_SHAPE, "k and in_pitch must be multiples of 16 and in_pitch >= k + 4 * sf_cols");
+    if (dst_sf_stride < n_dst) return fail(DG_ERR_SHAPE, "scale stride smaller than the row count");
+    if (n_dst == 0) return DG_OK;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_moe_unpack_rows_kernel<<<ceil_div(n_dst, 8), 256, 0, ctx->stream>>>(in, in_pitch, k, sf_cols, idx, n_dst, dst_data, dst_sf, dst_sf_stride);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_moe_combine(dg_ctx* ctx, const uint16_t* rows, size_t pitch, const int32_t* pos, const float* weights, uint32_t tokens, uint32_t topk,
+                   uint32_t n, uint16_t* out, size_t out_pitch) {
+    if (!ctx || !rows || !pos || !weights || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (n % 8 || pitch % 8 || out_pitch % 8 || !aligned16(rows) || !aligned16(out)) return fail(DG_ERR_SHAPE, "n and pitches must be multiples of 8 elements");
+    if (tokens == 0 || n == 0) return DG_OK;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    const uint64_t threads = static_cast<uint64_t>(tokens) * (n / 8);
+    dg::dg_moe_combine_kernel<<<static_cast<uint32_t>((threads + 255) / 256), 256, 0, ctx->stream>>>(rows, pitch, pos, weights, tokens, topk, n, out,
+                                                                                                    out_pitch);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }

@@ -158,6 +158,24 @@ int dg_group_ends_from_m_indices(dg_ctx* ctx, const int32_t* m_indices, uint32_t
 /* ops_sm100.rs:1338 (unpack_fp4_raw_dev) */
 int dg_unpack_fp4_raw(dg_ctx* ctx, const uint8_t* src, size_t packed_len, uint8_t* dst);
 
+/* Row movers either side of the expert-sharded grouped GEMM (the reference's single-GPU versions are
+ * deepgemm/src/cuda/layout.rs:174 gather_rows_fp8 and :192 scatter_rows_f32_acc; here they feed and
+ * drain an all-to-all).  All index arrays are device int32.
+ * dg_gather_rows: dst row i = src row idx[i] (row_bytes, multiple of 16); idx[i] < 0 writes zeros. */
+int dg_gather_rows(dg_ctx* ctx, const void* src, size_t src_pitch, const int32_t* idx, uint32_t n_dst, uint32_t row_bytes, void* dst,
+                   size_t dst_pitch);
+/* Send row i = [k e4m3 bytes of token idx[i] | its sf_cols packed scale words | zeros up to out_pitch]. */
+int dg_moe_pack_rows(dg_ctx* ctx, const uint8_t* data, uint32_t k, const uint32_t* sf, uint32_t sf_stride, uint32_t sf_cols, const int32_t* idx,
+                     uint32_t n, uint8_t* out, size_t out_pitch);
+/* Arena row i = received row idx[i]: data to dst_data (n_dst, k), scale words to the packed layout
+ * dst_sf[c * dst_sf_stride + i]; idx[i] < 0 (alignment padding) writes zero data and scales. */
+int dg_moe_unpack_rows(dg_ctx* ctx, const uint8_t* in, size_t in_pitch, uint32_t k, uint32_t sf_cols, const int32_t* idx, uint32_t n_dst,
+                       uint8_t* dst_data, uint32_t* dst_sf, uint32_t dst_sf_stride);
+/* out[t, :] = bf16(sum_j weights[t, j] * rows[pos[t, j], :]): f32, terms in order, one fused
+ * multiply-add each; pos < 0 skips a term.  rows / out are bf16 with pitches in elements. */
+int dg_moe_combine(dg_ctx* ctx, const uint16_t* rows, size_t pitch, const int32_t* pos, const float* weights, uint32_t tokens, uint32_t topk,
+                   uint32_t n, uint16_t* out, size_t out_pitch);
+
 /* deepgemm/src/types.rs:195-219 (mk alignment knob; process-global, power of two in [16,256]). */
 int dg_set_mk_alignment_for_contiguous_layout(uint32_t value);
 uint32_t dg_get_mk_alignment_for_contiguous_layout(void);

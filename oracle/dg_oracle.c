@@ -561,6 +561,22 @@ DGO_API void dgo_requant_fp8(const float* d, uint32_t rows, uint32_t n, uint32_t
         }
 }
 
+/* MoE combine (gather-reduce form of cuda/layout.rs:192-207 followed by :211 f32->bf16):
+ * out[t] = bf16(sum_j w[t,j] * rows[pos[t,j]]), f32 accumulation in order with fmaf; pos < 0 skipped. */
+DGO_API void dgo_moe_combine(const uint16_t* rows, size_t pitch, const int32_t* pos, const float* w, uint32_t tokens,
+                             uint32_t topk, uint32_t n, uint16_t* out) {
+    for (uint32_t t = 0; t < tokens; ++t)
+        for (uint32_t c = 0; c < n; ++c) {
+            float acc = 0.0f;
+            for (uint32_t j = 0; j < topk; ++j) {
+                int32_t p = pos[(size_t)t * topk + j];
+                if (p < 0) continue;
+                acc = fmaf(w[(size_t)t * topk + j], dgo_bf16_to_f32(rows[(size_t)p * pitch + c]), acc);
+            }
+            out[(size_t)t * n + c] = dgo_f32_to_bf16(acc);
+        }
+}
+
 /* 1 - 2*sum(xy)/sum(x^2+y^2) in f64 (the tolerance metric; the reference has
  * no such function, the benchmark contract defines it). */
 DGO_API double dgo_calc_diff(const float* x, const float* y, size_t n) {

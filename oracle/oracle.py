@@ -66,6 +66,7 @@ _mxfp4_ref = _sig("dgo_mxfp4_gemm_reference", None, _u8p, _u32p, C.c_uint32, _u8
 _dequant = _sig("dgo_dequant_rows", None, _u8p, _u32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                 C.c_uint32, _u32p, C.c_uint32, _f32p)
 _requant = _sig("dgo_requant_fp8", None, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, _u8p, _u32p)
+_moe_combine = _sig("dgo_moe_combine", None, _u16p, C.c_size_t, _i32p, _f32p, C.c_uint32, C.c_uint32, C.c_uint32, _u16p)
 _calc_diff = _sig("dgo_calc_diff", C.c_double, _f32p, _f32p, C.c_size_t)
 _max_threads = _sig("dgo_max_threads", C.c_int)
 
@@ -310,6 +311,18 @@ def requant_fp8(d, batch, n_total_rows_stride, out, sfd):
     d = np.ascontiguousarray(d, np.float32)
     rows, n = d.shape
     _requant(d, rows, n, batch, n_total_rows_stride, out, sfd)
+
+
+def moe_combine(rows_bits, pos, w):
+    """out[t] = bf16(sum_j w[t,j] * rows[pos[t,j]]) (cuda/layout.rs:192-216 as a gather-reduce); bf16 bit patterns in and out."""
+    rows_bits = np.ascontiguousarray(rows_bits, np.uint16)
+    pos = np.ascontiguousarray(pos, np.int32)
+    w = np.ascontiguousarray(w, np.float32)
+    tokens, topk = pos.shape
+    n = rows_bits.shape[1]
+    out = np.zeros((tokens, n), np.uint16)
+    _moe_combine(rows_bits, n, pos, w, tokens, topk, n, out)
+    return out
 
 
 def calc_diff(x, y):

@@ -1,0 +1,115 @@
+"""GPU parity of the MoE row movers (bit-exact against numpy / the oracle) and of one whole
+expert-parallel step on a single rank (dispatch -> grouped GEMMs -> combine)."""
+import numpy as np
+import pytest
+import torch
+
+import deepgemm_rust_b200 as dg
+from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel
+from oracle import oracle as O
+from tests.helpers import dev, fp8_operand_1d, fp8_operand_2d, to_f32
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = dg.DgContext(0)
+    yield c
+    c.sync()
+    c.close()
+
+
+def test_row_movers_bit_exact(ctx):
+    rng = np.random.default_rng(5)
+    rows, k, gran = 100, 1152, 128
+    cols, stride = dg.sf_packed_cols(k, gran), dg.sf_aligned_rows(rows)
+    xq = rng.integers(0, 256, (rows, k), dtype=np.uint8)
+    xsf = rng.integers(0, 2 ** 32, cols * stride, dtype=np.uint32)
+    idx = rng.integers(0, rows, 333).astype(np.int32)
+    pitch = (k + 4 * cols + 15) // 16 * 16
+    sent = dg.moe_pack_rows_dev(ctx, dev(xq), dev(xsf), rows, k, gran, dev(idx), pitch).cpu().numpy()
+    assert np.array_equal(sent[:, :k], xq[idx])
+    words = sent[:, k:k + 4 * cols].copy().view(np.uint32)
+    assert np.array_equal(words, xsf.reshape(cols, stride)[:, idx].T)
+    assert np.all(sent[:, k + 4 * cols:] == 0)
+    # unpack into an arena with padding rows
+    n_dst = 400
+    src = rng.integers(-1, 333, n_dst).astype(np.int32)
+    data, sf = dg.moe_unpack_rows_dev(ctx, dev(sent), k, gran, dev(src), n_dst)
+    data, sf = data.cpu().numpy(), sf.cpu().numpy().view(np.uint32).reshape(cols, dg.sf_aligned_rows(n_dst))
+    valid = src >= 0
+    assert np.array_equal(data[valid], sent[src[valid], :k]) and np.all(data[~valid] == 0)
+    assert np.array_equal(sf[:, :n_dst][:, valid], words[src[valid]].T) and np.all(sf[:, :n_dst][:, ~valid] == 0)
+    # generic gather of bf16 rows
+    y = rng.integers(0, 65536, (n_dst, 256), dtype=np.uint16)
+    got = dg.gather_rows_dev(ctx, dev(y, torch.bfloat16), dev(src), n_dst).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got[valid], y[src[valid]]) and np.all(got[~valid] == 0)
+    # weighted combine against the oracle (same fused multiply-add chain)
+    tokens, topk, n = 57, 8, 512
+    rows_bits = O.bf16_bits(rng.standard_normal((300, n)).astype(np.float32))
+    pos = rng.integers(-1, 300, (tokens, topk)).astype(np.int32)
+    w = rng.random((tokens, topk)).astype(np.float32)
+    got = dg.moe_combine_dev(ctx, dev(rows_bits, torch.bfloat16), dev(pos), dev(w)).view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got, O.moe_combine(rows_bits, pos, w))
+    ctx.sync()
+
+
+def test_expert_parallel_step_single_rank(ctx):
+    experts, topk, tokens, hidden, n1, k2, n2 = 8, 2, 200, 512, 256, 256, 384
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn((tokens, experts), generator=g)
+    probs = torch.softmax(logits, -1)
+    topw, topi = probs.topk(topk, dim=-1)
+    topi[:, 1] = torch.where(topi[:, 1] == 3, topi[:, 0], topi[:, 1])      # expert 3 may end up empty for some seeds
+    _, xq, xsf = fp8_operand_1d(tokens, hidden, 81)
+    _, w1q, w1sf, _ = fp8_operand_2d(experts * n1, hidden, 82, experts)
+    _, w2q, w2sf, _ = fp8_operand_2d(experts * n2, k2, 83, experts)
+    ep = ExpertParallel(experts, topk, DeviceRowOps(ctx))
+    plan = ep.plan(topi.cuda())
+    a, a_sf = ep.dispatch(plan, dev(xq), dev(xsf), hidden)
+    # arena rows hold exactly the routed tokens, grouped by expert, groups aligned to 128
+    m_idx = plan.m_indices.cpu().numpy()
+    flat = topi.reshape(-1).numpy()
+    order = np.argsort(flat, kind="stable")
+    arena = a.cpu().numpy()
+    starts = np.concatenate([[0], np.cumsum((np.bincount(flat, minlength=experts) + 127) // 128 * 128)[:-1]])
+    seen = np.zeros(experts, np.int64)
+    for p in order:
+        e, t = flat[p], p // topk
+        r = starts[e] + seen[e]
+        seen[e] += 1
+        assert m_idx[r] == e and np.array_equal(arena[r], xq[t])
+    assert int((m_idx >= 0).sum()) == tokens * topk and np.all(arena[m_idx < 0] == 0)
+    # grouped GEMM 1 on the arena against the oracle, on the valid rows
+    h = torch.zeros((plan.m_pad, n1), dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(a, a_sf, plan.m_pad, hidden, hidden), plan.m_indices,
+                                             dg.LpOperand(dev(w1q), dev(w1sf), experts * n1, hidden, hidden), dg.Sm100Out.Bf16(h, n1), experts)
+    ctx.sync()
+    valid = np.nonzero(m_idx >= 0)[0]
+    a_sf_np = a_sf.cpu().numpy().view(np.uint32)
+    hn = to_f32(h)
+    for e in range(experts):
+        rows = valid[m_idx[valid] == e].astype(np.uint32)
+        if rows.size == 0:
+            continue
+        want = O.lp_gemm_rows(arena, a_sf_np, 8, 128, 1, plan.m_pad, rows, w1q, w1sf, 8, 128, experts, n1,
+                              np.arange(e * n1, (e + 1) * n1, dtype=np.uint32), hidden)
+        assert O.calc_diff(hn[rows.astype(np.int64)], want) <= 2e-5
+    # grouped GEMM 2 takes an independent operand of the arena's row count (the benchmark's two GEMMs are independent)
+    _, actq, actsf = fp8_operand_1d(plan.m_pad, k2, 84)
+    y = torch.zeros((plan.m_pad, n2), dtype=torch.bfloat16, device="cuda")
+    dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(dev(actq), dev(actsf), plan.m_pad, k2, k2), plan.m_indices,
+                                             dg.LpOperand(dev(w2q), dev(w2sf), experts * n2, k2, k2), dg.Sm100Out.Bf16(y, n2), experts)
+    out = ep.combine(plan, y, topw.cuda().contiguous())
+    ctx.sync()
+    # combine: token t gets sum_j w[t,j] * y[arena row of pair (t,j)], bit-exact with the oracle reduction
+    y_bits = y.view(torch.int16).cpu().numpy().view(np.uint16)
+    pos = np.zeros((tokens, topk), np.int32)
+    seen[:] = 0
+    for p in order:
+        e = flat[p]
+        pos[p // topk, p % topk] = starts[e] + seen[e]
+        seen[e] += 1
+    want = O.moe_combine(y_bits, pos, topw.numpy())
+    assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want)
