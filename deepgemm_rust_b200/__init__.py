@@ -62,7 +62,7 @@ class _Desc(C.Structure):
 
 class _Config(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("swap_ab", "block_m", "block_n", "block_k", "cluster_m", "cluster_n", "num_stages",
-                                          "num_accum_stages", "smem_size", "num_tiles")]
+                                          "num_accum_stages", "smem_size", "num_tiles", "num_splits")]
 
 
 def _proto(name, restype, *argtypes):
@@ -439,6 +439,7 @@ class Sm100Config:
     num_accum_stages: int
     smem_size: int
     num_tiles: int
+    num_splits: int = 1
 
 
 SM100_SMEM_CAPACITY = 232448
@@ -451,4 +452,4 @@ def best_config(desc: Sm100Desc) -> Sm100Config:
     c = _Config()
     _check(_best_config(C.byref(d), C.byref(c)))
     return Sm100Config(bool(c.swap_ab), c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n, c.num_stages,
-                       c.num_accum_stages, c.smem_size, c.num_tiles)
+                       c.num_accum_stages, c.smem_size, c.num_tiles, c.num_splits)

@@ -69,6 +69,8 @@ struct dg_ctx {
     dg::Status* status = nullptr;       // device word block the kernels report into
     uint32_t* group_ends = nullptr;     // scratch for the contiguous layout's group-end table
     uint32_t group_ends_cap = 0;
+    float* splitk_ws = nullptr;         // scratch for the f32 partial products of K-split GEMMs
+    size_t splitk_ws_cap = 0;           // in floats
 };
 
 extern "C" {
@@ -113,6 +115,7 @@ int dg_ctx_destroy(dg_ctx* ctx) {
     cudaSetDevice(ctx->ordinal);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->group_ends) cudaFree(ctx->group_ends);
+    if (ctx->splitk_ws) cudaFree(ctx->splitk_ws);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return DG_OK;
@@ -186,16 +189,22 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
     const char* force_ctas = getenv("DG_CTAS");
     const char* force_stages = getenv("DG_STAGES");
 
-    uint32_t best_n = 0, best_accum = 0, best_tiles = 0, best_ctas = 0, best_stages = 0;
+    const char* force_splits = getenv("DG_SPLITS");
+    uint32_t best_n = 0, best_accum = 0, best_tiles = 0, best_ctas = 0, best_stages = 0, best_splits = 1;
     double best_cost = 0;
     for (uint32_t ctas = 1; ctas <= 2; ++ctas) {
         if (force_ctas && static_cast<uint32_t>(atoi(force_ctas)) != ctas) continue;
         const uint32_t tile_m = 128 * ctas;
-        // a CTA pair needs 256-row tiles that stay inside one group
-        if (ctas == 2 && d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS && align % 256 != 0) continue;
+        // contiguous layout: a 256-row pair tile may run past its group's end; the rows beyond it are computed but
+        // never stored (groups start on multiples of 128, stores are 32 rows tall), so any 128-multiple alignment works
+        if (ctas == 2 && d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS && align % 128 != 0) continue;
         if (ctas == 2 && sms < 2) continue;
         uint32_t m_blocks;
-        if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) m_blocks = ceil_div(d->m, tile_m);
+        if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) {
+            // groups are padded to the alignment and every group rounds up to whole tiles
+            const uint32_t per_group = groups ? d->m / groups : d->m;
+            m_blocks = groups * ceil_div(per_group ? per_group : 1, tile_m);
+        }
         else if (d->gemm_type == DG_GEMM_M_GROUPED_MASKED) m_blocks = groups * ceil_div(d->expected_m ? d->expected_m : d->m, tile_m);
         else m_blocks = groups * ceil_div(d->m, tile_m);
         const uint32_t workers = sms / ctas;
@@ -205,24 +214,40 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
             const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
             if (bn + sf_cols > 512) continue;
             const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
-            uint32_t stages = force_stages ? static_cast<uint32_t>(atoi(force_stages)) : dg::kMaxStages;
-            if (stages > dg::kMaxStages) stages = dg::kMaxStages;
-            while (stages > 1 && dg::gemm_smem_bytes(bn, ctas, d->cd_dtype, stages, sfa_words, sfb_words) > kSmemCapacity) --stages;
-            if (stages < 1 || dg::gemm_smem_bytes(bn, ctas, d->cd_dtype, stages, sfa_words, sfb_words) > kSmemCapacity) continue;
-            if (stages < 3 && !force_stages) continue;
             const uint32_t tiles = m_blocks * ceil_div(d->n, bn);
-            const uint32_t waves = ceil_div(tiles, workers);
-            // cycles per tile.  One UMMA (K = 32 bytes) costs max(~118, bn / 2) cycles on its CTA's tensor core
-            // (measured issue floor / 8192 MACs per cycle); the loads of a k-block (A 16 KB + B bn/ctas x 128 B)
-            // must also arrive, at roughly 64 bytes per cycle per SM when every SM streams from L2.
-            const double k_blocks = ceil_div(d->k, block_k);
+            // cycles per tile, fitted to measurements on B200 (dense 4096x7168x4096, every width, 1 and 2 CTAs):
+            // per k-block max(UMMA time, load time) + ~150 of issue-side overhead, where one UMMA (K = 32 bytes) takes
+            // max(~118, bn / 2) cycles and a CTA receives its A tile (16 KB) plus bn/ctas rows of B at ~77 bytes per cycle;
+            // a single-buffered accumulator exposes the whole epilogue (~10.5 cycles per column).
+            const uint32_t total_kb = ceil_div(d->k, block_k);
             const double mma = 4.0 * (bn * 0.5 > 118.0 ? bn * 0.5 : 118.0);
-            const double feed = (16384.0 + bn / ctas * 128.0) / 64.0;
-            const double epilogue = accum == 1 ? 9.0 * bn : 1.0 * bn;  // not hidden behind the next tile when single-buffered
-            const double tile_cost = k_blocks * (mma > feed ? mma : feed) + epilogue + 600.0;
-            const double cost = waves * tile_cost;
-            if (best_n == 0 || cost < best_cost * (1.0 - 1e-9)) {
-                best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; best_ctas = ctas; best_stages = stages;
+            const double feed = (16384.0 + bn / ctas * 128.0) / 77.0;
+            const double epilogue = accum == 1 ? 10.5 * bn : 1.0 * bn;
+            const double per_kb = (mma > feed ? mma : feed) + 150.0;
+            // K ranges (dense GEMMs with f32-summable outputs only): each range is a multiple of 4 k-blocks so scale words
+            // never straddle ranges; the partial sums cost a second small kernel (launch + S reads of the M x N f32 tile set)
+            const bool may_split = d->gemm_type == DG_GEMM_NORMAL && d->cd_dtype != DG_OUT_FP8 && d->n % 4 == 0;
+            for (uint32_t splits = 1; splits <= 16; ++splits) {
+                if (splits > 1 && !may_split) break;
+                if (force_splits && static_cast<uint32_t>(atoi(force_splits)) != splits) continue;
+                uint32_t kb_per = ceil_div(ceil_div(total_kb, splits), 4) * 4;
+                if (splits > 1 && (kb_per < 8 || kb_per * (splits - 1) >= total_kb)) continue;   // every range non-empty, at least 8 k-blocks
+                if (splits == 1) kb_per = total_kb;
+                // K ranges store f32 partials whatever the caller's output type: size the staging buffers for that
+                const uint32_t kernel_out = splits > 1 ? static_cast<uint32_t>(DG_OUT_F32) : d->cd_dtype;
+                uint32_t stages = force_stages ? static_cast<uint32_t>(atoi(force_stages)) : dg::kMaxStages;
+                if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+                while (stages > 1 && dg::gemm_smem_bytes(bn, ctas, kernel_out, stages, sfa_words, sfb_words) > kSmemCapacity) --stages;
+                if (stages < 1 || dg::gemm_smem_bytes(bn, ctas, kernel_out, stages, sfa_words, sfb_words) > kSmemCapacity) continue;
+                if (stages < 3 && !force_stages) continue;
+                const uint32_t waves = ceil_div(tiles * splits, workers);
+                const double tile_cost = kb_per * per_kb + (splits > 1 ? 2.0 * bn : epilogue) + 600.0;
+                const double reduce = splits > 1 ? 9000.0 + static_cast<double>(splits) * d->m * d->n * 4.0 / 3000.0 : 0.0;
+                const double cost = waves * tile_cost + reduce;
+                if (best_n == 0 || cost < best_cost * (1.0 - 1e-9)) {
+                    best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; best_ctas = ctas; best_stages = stages;
+                    best_splits = splits;
+                }
             }
         }
     }
@@ -236,8 +261,9 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
     out->cluster_n = 1;
     out->num_stages = stages;
     out->num_accum_stages = best_accum;
-    out->smem_size = dg::gemm_smem_bytes(best_n, best_ctas, d->cd_dtype, stages, sfa_words, sfb_words);
+    out->smem_size = dg::gemm_smem_bytes(best_n, best_ctas, best_splits > 1 ? static_cast<uint32_t>(DG_OUT_F32) : d->cd_dtype, stages, sfa_words, sfb_words);
     out->num_tiles = best_tiles;
+    out->num_splits = best_splits;
     return DG_OK;
 }
 
@@ -368,6 +394,17 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
 
     const bool mxf4 = a->bits == 4;
     const uint32_t block_k = cfg.block_k;
+    const uint32_t splits = cfg.num_splits;
+    const uint32_t ws_pitch = align4(pr.n);
+    if (splits > 1) {
+        const size_t need = static_cast<size_t>(splits) * pr.m * ws_pitch;
+        if (ctx->splitk_ws_cap < need) {
+            DG_CUDA(cudaSetDevice(ctx->ordinal));
+            if (ctx->splitk_ws) { cudaFree(ctx->splitk_ws); ctx->splitk_ws = nullptr; ctx->splitk_ws_cap = 0; }
+            DG_CUDA(cudaMalloc(&ctx->splitk_ws, need * sizeof(float)));
+            ctx->splitk_ws_cap = need;
+        }
+    }
     const uint32_t sfa_words = 4 * a->gran_k >= block_k ? 1 : block_k / (4 * a->gran_k);
     const uint32_t sfb_words = 4 * b->gran_k >= block_k ? 1 : block_k / (4 * b->gran_k);
     const uint32_t sf_block_n = ceil_div(cfg.block_n, 128) * 128;
@@ -401,15 +438,23 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         if (rc) return rc;
     }
     {
-        const CUtensorMapDataType dt = out->kind == DG_OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                       : (out->kind == DG_OUT_FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-        const uint64_t pitch = static_cast<uint64_t>(out->ld) * d_elem;
-        uint64_t dims[3] = {pr.n, pr.m, a_groups};
-        uint64_t strides[2] = {pitch, pitch * pr.m};
         // 32 rows per store; 32 columns of bf16 (64-byte rows) or f32, 128 columns of e4m3 (128-byte rows)
-        uint32_t box[3] = {out->kind == DG_OUT_FP8 ? 128u : 32u, 32, 1};
-        rc = encode_map(&maps[4], dt, 3, out->buf, dims, strides, box,
-                        out->kind == DG_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, "D");
+        if (splits > 1) {
+            // K ranges write f32 partial tiles into the workspace, one plane per range
+            uint64_t dims[3] = {pr.n, pr.m, splits};
+            uint64_t strides[2] = {static_cast<uint64_t>(ws_pitch) * 4, static_cast<uint64_t>(ws_pitch) * 4 * pr.m};
+            uint32_t box[3] = {32, 32, 1};
+            rc = encode_map(&maps[4], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ctx->splitk_ws, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "D partials");
+        } else {
+            const CUtensorMapDataType dt = out->kind == DG_OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                           : (out->kind == DG_OUT_FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+            const uint64_t pitch = static_cast<uint64_t>(out->ld) * d_elem;
+            uint64_t dims[3] = {pr.n, pr.m, a_groups};
+            uint64_t strides[2] = {pitch, pitch * pr.m};
+            uint32_t box[3] = {out->kind == DG_OUT_FP8 ? 128u : 32u, 32, 1};
+            rc = encode_map(&maps[4], dt, 3, out->buf, dims, strides, box,
+                            out->kind == DG_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, "D");
+        }
         if (rc) return rc;
     }
 
@@ -421,6 +466,9 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.num_groups = pr.groups;
     p.gemm_type = pr.type;
     p.block_n = cfg.block_n;
+    p.block_k_elems = block_k;
+    p.num_splits = splits;
+    p.kb_per_split = splits > 1 ? ceil_div(ceil_div(ceil_div(pr.k, block_k), splits), 4) * 4 : ceil_div(pr.k, block_k);
     p.num_stages = cfg.num_stages;
     p.num_accum_stages = cfg.num_accum_stages;
     p.gran_a = a->gran_k;
@@ -428,7 +476,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.sf_a_cols = sfa_cols;
     p.sf_b_cols = sfb_cols;
     p.mk_alignment = align;
-    p.has_alpha = e.has_alpha ? 1 : 0;
+    p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges alpha is applied to the sum
     p.alpha = e.alpha;
     p.sfd = out->sfd;
     p.sfd_stride = align4(pr.m);
@@ -445,13 +493,25 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
 
     const uint32_t ctas = cfg.cluster_m;
     uint32_t grid = static_cast<uint32_t>(ctx->num_sms) / ctas * ctas;
-    if (pr.type == DG_GEMM_NORMAL || pr.type == DG_GEMM_BATCHED) grid = cfg.num_tiles * ctas < grid ? cfg.num_tiles * ctas : grid;
+    if (pr.type == DG_GEMM_NORMAL || pr.type == DG_GEMM_BATCHED)
+        grid = cfg.num_tiles * splits * ctas < grid ? cfg.num_tiles * splits * ctas : grid;
+    const int kernel_out = splits > 1 ? DG_OUT_F32 : out->kind;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     cudaError_t ce;
-    if (mxf4) ce = ctas == 2 ? launch_by_out<true, 2>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps)
-                             : launch_by_out<true, 1>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps);
-    else ce = ctas == 2 ? launch_by_out<false, 2>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps)
-                        : launch_by_out<false, 1>(out->kind, p, grid, cfg.smem_size, ctx->stream, maps);
+    if (mxf4) ce = ctas == 2 ? launch_by_out<true, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
+                             : launch_by_out<true, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
+    else ce = ctas == 2 ? launch_by_out<false, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
+                        : launch_by_out<false, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
+    if (ce == cudaSuccess && splits > 1) {
+        const uint64_t threads = static_cast<uint64_t>(pr.m) * ceil_div(pr.n, 4);
+        const uint32_t blocks = static_cast<uint32_t>((threads + 255) / 256);
+        const float alpha = e.has_alpha ? e.alpha : 1.0f;
+        if (out->kind == DG_OUT_BF16)
+            dg::dg_splitk_reduce_kernel<true><<<blocks, 256, 0, ctx->stream>>>(ctx->splitk_ws, splits, pr.m, pr.n, ws_pitch, alpha, out->buf, out->ld);
+        else
+            dg::dg_splitk_reduce_kernel<false><<<blocks, 256, 0, ctx->stream>>>(ctx->splitk_ws, splits, pr.m, pr.n, ws_pitch, alpha, out->buf, out->ld);
+        ce = cudaGetLastError();
+    }
     if (ce != cudaSuccess) return fail(DG_ERR_DRIVER, "kernel launch failed: %s", cudaGetErrorString(ce));
     return DG_OK;
 }

@@ -212,6 +212,35 @@ __global__ void __launch_bounds__(1024) dg_group_ends_scan_kernel(uint32_t* ends
     }
 }
 
+// Sum of the f32 partial products of a K-split GEMM: out[m, n] = alpha * sum_s partial[s, m, n], added in order
+// s = 0, 1, ... (deterministic), written as bf16 or f32.  One thread owns 4 columns (16-byte loads).
+template <bool kBf16>
+__global__ void __launch_bounds__(256) dg_splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, uint32_t m, uint32_t n,
+                                                               uint32_t pitch, float alpha, void* __restrict__ out, uint32_t out_ld) {
+    const uint32_t chunks = (n + 3) / 4;
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<uint64_t>(m) * chunks) return;
+    const uint32_t row = static_cast<uint32_t>(i / chunks), c = static_cast<uint32_t>(i % chunks) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t s = 0; s < splits; ++s) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * m + row) * pitch + c));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= alpha; acc.y *= alpha; acc.z *= alpha; acc.w *= alpha;
+    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+    if constexpr (kBf16) {
+        uint16_t* o = static_cast<uint16_t*>(out) + static_cast<size_t>(row) * out_ld + c;
+        if (c + 4 <= n && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
+            *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16x2(vals[0], vals[1]), pack_bf16x2(vals[2], vals[3]));
+        } else {
+            for (uint32_t j = 0; j < 4 && c + j < n; ++j) o[j] = static_cast<uint16_t>(pack_bf16x2(vals[j], 0.f) & 0xFFFF);
+        }
+    } else {
+        float* o = static_cast<float*>(out) + static_cast<size_t>(row) * out_ld + c;
+        for (uint32_t j = 0; j < 4 && c + j < n; ++j) o[j] = vals[j];
+    }
+}
+
 // Packed e2m1 -> one code per byte (low nibble), 16 bytes in, 32 bytes out per thread.
 __global__ void __launch_bounds__(256) dg_unpack_fp4_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t packed_len) {
     const uint64_t i = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 16;

@@ -44,10 +44,13 @@ struct GemmParams {
     uint32_t num_groups;
     uint32_t gemm_type;
     uint32_t block_n;
+    uint32_t block_k_elems;    // 128 (e4m3) or 256 (packed e2m1)
     uint32_t num_stages;
     uint32_t num_accum_stages;
     uint32_t gran_a, gran_b;   // K elements per scale factor (32 or 128)
     uint32_t sf_a_cols, sf_b_cols;  // packed words per row (per group) along K
+    uint32_t num_splits;       // dense only: K is cut into this many ranges, each writing its own f32 partial (D's 3rd coordinate)
+    uint32_t kb_per_split;     // k-blocks per range (a multiple of every scale-word period)
     uint32_t mk_alignment;     // contiguous layout: every group starts at a multiple of this
     uint32_t has_alpha;
     float alpha;
@@ -71,7 +74,10 @@ struct GemmParams {
 
 struct Tile {
     uint32_t m0, n0;     // first row / column of the tile (row is group-local except in the contiguous arena)
-    uint32_t ga, gb;     // group coordinate of A/D and of B
+    uint32_t m_end;      // rows at or beyond this one belong to someone else (next group / out of range): never stored
+    uint32_t ga, gb;     // group coordinate of A/SFA and of B/SFB
+    uint32_t gd;         // third coordinate of D: the group, or the K range when K is split
+    uint32_t kb0, kb1;   // k-block range of this tile
 };
 
 // Walks the tile list of one CTA.  Every role runs its own copy and sees the same sequence.
@@ -79,7 +85,7 @@ struct Scheduler {
     const GemmParams& p;
     uint32_t tile_m, worker, num_workers;   // rows per tile; CTA (or CTA pair) index and count
     uint32_t num_m_blocks, num_n_blocks, iter;
-    uint32_t cur_group, cum_begin, cur_m_blocks, cur_row_start;
+    uint32_t cur_group, cum_begin, cur_m_blocks, cur_row_start, cur_row_end;
 
     DG_DEVICE Scheduler(const GemmParams& params, uint32_t ctas) : p(params) {
         tile_m = kBlockM * ctas;
@@ -92,6 +98,7 @@ struct Scheduler {
         cum_begin = 0;
         cur_m_blocks = 0;
         cur_row_start = 0;
+        cur_row_end = p.m;
         if (p.gemm_type == kGemmContiguous || p.gemm_type == kGemmMasked) load_group();
     }
 
@@ -102,20 +109,35 @@ struct Scheduler {
             const uint32_t end = __ldg(p.grouped_layout + cur_group);
             cur_row_start = (prev_end + p.mk_alignment - 1) / p.mk_alignment * p.mk_alignment;
             const uint32_t rows = end > cur_row_start ? end - cur_row_start : 0u;
+            cur_row_end = end < p.m ? end : p.m;
             cur_m_blocks = (rows + tile_m - 1) / tile_m;
         } else {
             const int32_t valid = static_cast<int32_t>(__ldg(p.grouped_layout + cur_group));
             const uint32_t rows = valid <= 0 ? 0u : (static_cast<uint32_t>(valid) < p.m ? static_cast<uint32_t>(valid) : p.m);
             cur_row_start = 0;
+            cur_row_end = p.m;
             cur_m_blocks = (rows + tile_m - 1) / tile_m;
         }
     }
 
     DG_DEVICE bool next(Tile& t) {
-        const uint32_t idx = worker + (iter++) * num_workers;
+        uint32_t idx = worker + (iter++) * num_workers;
+        const uint32_t total_kb = (p.k + p.block_k_elems - 1) / p.block_k_elems;
+        t.kb0 = 0;
+        t.kb1 = total_kb;
         if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmBatched) {
             const uint32_t per_group = num_m_blocks * num_n_blocks;
-            if (idx >= per_group * p.num_groups) return false;
+            uint32_t split = 0;
+            if (p.num_splits > 1) {
+                // K ranges of one output tile sit next to each other in the tile order
+                if (idx >= per_group * p.num_splits) return false;
+                split = idx % p.num_splits;
+                idx /= p.num_splits;
+                t.kb0 = split * p.kb_per_split;
+                t.kb1 = t.kb0 + p.kb_per_split < total_kb ? t.kb0 + p.kb_per_split : total_kb;
+            } else if (idx >= per_group * p.num_groups) {
+                return false;
+            }
             const uint32_t g = idx / per_group, r = idx - g * per_group;
             // bands of 16 row-blocks, rows fastest inside a band: the tiles in flight at
             // any moment form a compact patch, so A and B tiles are re-read from L2
@@ -126,8 +148,10 @@ struct Scheduler {
             const uint32_t rows_here = num_m_blocks - first_m < kBand ? num_m_blocks - first_m : kBand;
             const uint32_t nb = in_band / rows_here, mb = first_m + (in_band - nb * rows_here);
             t.m0 = mb * tile_m;
+            t.m_end = p.m;
             t.n0 = nb * p.block_n;
             t.ga = t.gb = g;
+            t.gd = p.num_splits > 1 ? split : g;
             return true;
         }
         while (true) {
@@ -141,9 +165,11 @@ struct Scheduler {
         const uint32_t in_group = idx - cum_begin;
         const uint32_t nb = in_group / cur_m_blocks, ml = in_group - nb * cur_m_blocks;
         t.m0 = cur_row_start + ml * tile_m;
+        t.m_end = cur_row_end;
         t.n0 = nb * p.block_n;
         t.gb = cur_group;
         t.ga = p.gemm_type == kGemmContiguous ? 0u : cur_group;
+        t.gd = t.ga;
         return true;
     }
 };
@@ -183,7 +209,6 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     const uint32_t sfa_bytes = 512 * plan_a.words, sfb_bytes = sf_block_n * 4 * plan_b.words;
     const uint32_t a_bytes = kBlockM * kBlockKBytes, b_bytes = load_n * kBlockKBytes;
     const uint32_t num_stages = p.num_stages;
-    const uint32_t num_k_blocks = (p.k + kBlockKElems - 1) / kBlockKElems;
 
     // shared memory carve-up (every tile base stays 1024-byte aligned)
     uint8_t* smem_a = smem;
@@ -245,7 +270,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         while (ok && sched.next(t)) {
             const int32_t row_a = static_cast<int32_t>(t.m0 + cta_rank * kBlockM);
             const int32_t row_b = static_cast<int32_t>(t.n0 + cta_rank * load_n);
-            for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
                 bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
 #ifdef DG_PROFILE
@@ -299,7 +324,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 DG_PROF_ADD(4, t_acc);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + e * block_n;
-                for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+                for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                     bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
 #ifdef DG_PROFILE
                     if (p.debug_flags & 2) need_a = need_b = false;
@@ -335,7 +360,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         idescs[k] = idesc_with_sf_ids(idesc, a_id, b_id);
                     }
                     const uint64_t sfa_desc = make_smem_desc(sfa_addr, 0, 128, 0), sfb_desc = make_smem_desc(sfb_addr, 0, 128, 0);
-                    const bool last = kb + 1 == num_k_blocks;
+                    const bool last = kb + 1 == t.kb1;
                     if (elect_one()) {
                         if (need_a)
                             for (uint32_t c = 0; c < plan_a.words; ++c) utccp_32x128b_warpx4<kCtas>(tmem_sfa + 4 * c, sfa_desc + c * (512 >> 4));
@@ -344,7 +369,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         #pragma unroll
                         for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
                             umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
-                                                            a_cols[k], b_cols[k], (kb | k) != 0 ? 1u : 0u);
+                                                            a_cols[k], b_cols[k], (kb != t.kb0 || k != 0) ? 1u : 0u);
                         if constexpr (kCtas == 1) {
                             umma_commit(bar_empty + stage);
                             if (last) umma_commit(bar_tmem_full + e);
@@ -372,7 +397,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         uint32_t stage = 0, sf_phase_bits = 0;
         bool ok = true;
         while (ok && sched.next(t)) {
-            for (uint32_t kb = 0; kb < num_k_blocks; ++kb) {
+            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
@@ -507,15 +532,15 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 if (sub_in_buf + 1 == kSubsPerBuf) {
                     const uint32_t col0 = t.n0 + (s / kSubsPerBuf) * kColsPerBuf;
                     if constexpr (kOut == kOutFp8) {
-                        if (row < p.m && col0 < p.n)
+                        if (row < t.m_end && col0 < p.n)
                             p.sfd[static_cast<size_t>(t.ga * (p.n / 128) + col0 / 128) * p.sfd_stride + row] = sf_word;
                         sf_word = 0;
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (col0 < p.n && row0 < p.m)
-                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.ga));
+                        if (col0 < p.n && row0 < t.m_end)
+                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.gd));
                         tma_store_commit();
                     }
                     buf_idx ^= 1;

@@ -199,6 +199,7 @@ typedef struct {
     uint32_t num_accum_stages;   /* TMEM accumulator buffers (2 = epilogue overlaps the next tile) */
     uint32_t smem_size;
     uint32_t num_tiles;          /* expected tiles (from expected_m for grouped layouts) */
+    uint32_t num_splits;         /* dense GEMMs with few tiles: K ranges computed by different CTAs and summed in f32 */
 } dg_config;
 /* heuristics_sm100.rs:455 (best_config) */
 int dg_best_config(const dg_desc* desc, dg_config* out);

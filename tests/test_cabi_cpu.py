@@ -80,6 +80,12 @@ def test_heuristics_grouped_and_output_kinds():
     # skinny problems get narrow tiles so more SMs have work
     c = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 2112, 7168))
     assert c.block_n <= 128
+    # ... and a long K with few tiles is cut into K ranges; grouped and FP8-output GEMMs never are
+    c = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 7168, 16384))
+    assert c.num_splits > 1 and c.num_tiles * c.num_splits >= 100
+    assert dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 4096, 7168, 16384)).num_splits == 1
+    assert dg.best_config(dg.Sm100Desc(dg.GemmType.MGroupedMasked, 128, 4096, 16384, num_groups=2, expected_m=64)).num_splits == 1
+    assert dg.best_config(dg.Sm100Desc(dg.GemmType.Batched, 128, 1024, 16384, num_groups=2, cd_dtype=2)).num_splits == 1
     with pytest.raises(dg.DgError):
         dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 128, 128, a_bits=8, b_bits=4))
 

@@ -92,6 +92,18 @@ def test_dense_fp8_every_tile_shape(ctx, ctas, block_n, monkeypatch):
     run_dense(ctx, 600, 1000, 1152, out_kind=1, seed=block_n + ctas)
 
 
+@pytest.mark.parametrize("splits", [2, 3, 5])
+def test_dense_fp8_split_k(ctx, splits, monkeypatch):
+    # K ranges computed by different CTAs, f32 partials summed by a second kernel; ranges are multiples of 4 k-blocks,
+    # the last one may be shorter (K = 36 k-blocks here)
+    monkeypatch.setenv("DG_SPLITS", str(splits))
+    cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 1000, 4608))
+    assert cfg.num_splits == splits
+    run_dense(ctx, 128, 1000, 4608, seed=splits)
+    run_dense(ctx, 100, 512, 4608, out_kind=1, seed=splits, alpha=0.5)
+    run_dense(ctx, 300, 256, 9216, out_kind=0, seed=splits, alpha=2.0)
+
+
 def test_dense_fp8_matches_scalar_reference_and_golden(ctx):
     # the committed fixture holds quantised inputs of the 128x256x512 case and the output of the scalar
     # restatement of ref_fp8_gemm_nt (f32); the GPU f32 output must agree with it
@@ -165,7 +177,11 @@ def contiguous_layout(group_sizes, alignment=128):
     ([37, 128, 1, 64, 15, 100, 128, 3], 384, 1024),
     ([200, 0, 300, 0, 0, 129], 512, 768),       # empty experts, multi-tile experts
 ])
-def test_m_grouped_contiguous(ctx, sizes, n, k):
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_m_grouped_contiguous(ctx, sizes, n, k, ctas, monkeypatch):
+    # with a CTA pair the 256-row tile of a group's tail reaches into the next group's rows: those rows are
+    # computed but must never be stored
+    monkeypatch.setenv("DG_CTAS", str(ctas))
     groups = len(sizes)
     m_idx, starts = contiguous_layout(sizes)
     m_total = len(m_idx)
@@ -179,6 +195,10 @@ def test_m_grouped_contiguous(ctx, sizes, n, k):
     dn = to_f32(d)
     valid = np.nonzero(m_idx >= 0)[0]
     assert not np.isnan(dn[valid]).any()
+    # rows of empty 128-row slots (whole slots of padding) are never touched
+    for slot in range(m_total // 128):
+        if np.all(m_idx[slot * 128:(slot + 1) * 128] < 0):
+            assert np.isnan(dn[slot * 128:(slot + 1) * 128]).all()
     # the scalar restatement of ref_m_grouped_fp8_gemm_nt_contiguous on every valid row (per-expert tile scales)
     kb = k // 128
     sfa = np.stack([O.exps_to_f32(((asf.reshape(-1, dg.sf_aligned_rows(m_total))[c // 4] >> ((c % 4) * 8)) & 0xFF).astype(np.uint8))
@@ -194,12 +214,14 @@ def test_m_grouped_contiguous(ctx, sizes, n, k):
     assert torch.equal(d[torch.from_numpy(valid).cuda()], d2[torch.from_numpy(valid).cuda()])
 
 
+@pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("masked,m_max,n,k", [
     ([37, 128, 1, 64, 15, 100, 128, 3], 128, 256, 512),   # reference fixture (tests/e2e.rs:131,566)
     ([0, 256, 17, 129, 255, 16, 0, 1], 256, 384, 1024),
     ([100, 7], 100, 128, 256),                               # m_max not a multiple of the tile
 ])
-def test_m_grouped_masked(ctx, masked, m_max, n, k):
+def test_m_grouped_masked(ctx, masked, m_max, n, k, ctas, monkeypatch):
+    monkeypatch.setenv("DG_CTAS", str(ctas))
     groups = len(masked)
     masked_m = np.array(masked, np.int32)
     _, aq, asf = fp8_operand_1d(groups * m_max, k, 21, 128, groups)
@@ -223,7 +245,7 @@ def test_m_grouped_masked(ctx, masked, m_max, n, k):
     assert diff <= TIGHT_BF16, diff
     # rows of a group whose tiles were never scheduled keep the caller's contents (no stray writes)
     for g in range(groups):
-        first_untouched = g * m_max + ((masked[g] + 127) // 128) * 128
+        first_untouched = g * m_max + ((masked[g] + 128 * ctas - 1) // (128 * ctas)) * 128 * ctas
         if first_untouched < (g + 1) * m_max:
             assert np.isnan(dn[first_untouched:(g + 1) * m_max]).all()
 
