@@ -107,6 +107,7 @@ _gather_rows = _proto("dg_gather_rows", C.c_int, _vp, _vp, _sz, _vp, _u32, _u32,
 _moe_pack = _proto("dg_moe_pack_rows", C.c_int, _vp, _vp, _u32, _vp, _u32, _u32, _vp, _u32, _vp, _sz)
 _moe_unpack = _proto("dg_moe_unpack_rows", C.c_int, _vp, _vp, _sz, _u32, _u32, _vp, _u32, _vp, _vp, _u32)
 _moe_combine = _proto("dg_moe_combine", C.c_int, _vp, _vp, _sz, _vp, _vp, _u32, _u32, _u32, _vp, _sz)
+_expire_wait = _proto("dg_debug_expire_wait", C.c_int, _vp, _u32)
 _set_mk = _proto("dg_set_mk_alignment_for_contiguous_layout", C.c_int, _u32)
 _get_mk = _proto("dg_get_mk_alignment_for_contiguous_layout", _u32)
 _get_mk_theory = _proto("dg_get_theoretical_mk_alignment_for_contiguous_layout", _u32, _u32)
@@ -392,6 +393,11 @@ def moe_combine_dev(ctx, rows: torch.Tensor, pos: torch.Tensor, weights: torch.T
     _check(_moe_combine(ctx._h, _vp(rows.data_ptr()), rows.stride(0), _vp(pos.data_ptr()), _vp(weights.data_ptr()), tokens, topk, n,
                         _vp(out.data_ptr()), out.stride(0)))
     return out
+
+
+def debug_expire_wait(ctx, limit_us: int = 1000):
+    """Launches the bounded-wait self-test; the following ctx.sync() raises DgError(Timeout) once."""
+    _check(_expire_wait(ctx._h, limit_us))
 
 
 def set_mk_alignment_for_contiguous_layout(value: int):

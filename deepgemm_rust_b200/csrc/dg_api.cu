@@ -752,6 +752,15 @@ int dg_unpack_fp4_raw(dg_ctx* ctx, const uint8_t* src, size_t packed_len, uint8_
     return DG_OK;
 }
 
+int dg_debug_expire_wait(dg_ctx* ctx, uint32_t limit_us) {
+    if (!ctx) return fail(DG_ERR_SHAPE, "null context");
+    if (limit_us == 0 || limit_us > 1000000) return fail(DG_ERR_SHAPE, "limit must be between 1 us and 1 s");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_expire_wait_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status, static_cast<uint64_t>(limit_us) * 1000ull);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
 // ------------------------------------------------------------------ MoE row movers
 static bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
 

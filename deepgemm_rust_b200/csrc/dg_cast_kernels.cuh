@@ -241,6 +241,21 @@ __global__ void __launch_bounds__(256) dg_splitk_reduce_kernel(const float* __re
     }
 }
 
+// Self-test of the bounded wait every kernel of this library uses: one warp waits on a barrier nothing will ever
+// arrive on, with a short limit.  The wait must give up, record (code, block, site) in the status block and let the
+// kernel finish normally, leaving the context usable.
+__global__ void dg_expire_wait_kernel(Status* status, uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    mbar_wait(&bar, 0, &abort_flag, status, 0x700, limit_ns);
+}
+
 // Packed e2m1 -> one code per byte (low nibble), 16 bytes in, 32 bytes out per thread.
 __global__ void __launch_bounds__(256) dg_unpack_fp4_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t packed_len) {
     const uint64_t i = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 16;

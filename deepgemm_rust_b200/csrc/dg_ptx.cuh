@@ -67,7 +67,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legal wa
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives
 // up; the others see it within a few hundred polls and leave as well.
-DG_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, Status* status, uint32_t site) {
+DG_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag, Status* status, uint32_t site,
+                         uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_ns();
     uint32_t polls = 0;
@@ -75,7 +76,7 @@ DG_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abor
         if (mbar_try_wait(bar, parity)) return true;
         if ((++polls & 0xFF) == 0) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > kWaitLimitNs) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status != nullptr && atomicCAS(&status->code, 0u, kStatusTimeout) == 0u) {
                     status->block = blockIdx.x;

@@ -176,6 +176,12 @@ int dg_moe_unpack_rows(dg_ctx* ctx, const uint8_t* in, size_t in_pitch, uint32_t
 int dg_moe_combine(dg_ctx* ctx, const uint16_t* rows, size_t pitch, const int32_t* pos, const float* weights, uint32_t tokens, uint32_t topk,
                    uint32_t n, uint16_t* out, size_t out_pitch);
 
+/* No counterpart in the reference (its device waits spin without bound, deepgemm/src/cuda/common.rs:74-85).
+ * Self-test of the bounded wait all kernels here use: launches one warp that waits, for at most limit_us, on a
+ * barrier nothing signals.  The kernel finishes normally; the next dg_ctx_sync returns DG_ERR_TIMEOUT (site 0x700)
+ * and clears the record, after which the context works as before. */
+int dg_debug_expire_wait(dg_ctx* ctx, uint32_t limit_us);
+
 /* deepgemm/src/types.rs:195-219 (mk alignment knob; process-global, power of two in [16,256]). */
 int dg_set_mk_alignment_for_contiguous_layout(uint32_t value);
 uint32_t dg_get_mk_alignment_for_contiguous_layout(void);

@@ -381,3 +381,15 @@ def test_argument_errors(ctx):
     finally:
         dg.set_mk_alignment_for_contiguous_layout(128)
     ctx.sync()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    # a wait nothing satisfies must end by itself, surface as a Timeout error on the host and leave the context usable
+    c = dg.DgContext(0)
+    dg.debug_expire_wait(c, 1000)
+    with pytest.raises(dg.DgError) as e:
+        c.sync()
+    assert e.value.kind == "Timeout" and "0x700" in str(e.value)
+    c.sync()                                  # the record is cleared by the report
+    run_dense(c, 128, 256, 512)               # and the same context still computes correctly
+    c.close()
