@@ -178,11 +178,9 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
     if ((d->a_bits != 8 && d->a_bits != 4) || (d->b_bits != 8 && d->b_bits != 4)) return fail(DG_ERR_SHAPE, "operand bits must be 8 or 4");
     if (d->a_bits != d->b_bits) return fail(DG_ERR_UNSUPPORTED, "mixed FP8 x FP4 operands are not built yet");
     const bool mxf4 = d->a_bits == 4;
-    const uint32_t block_k = mxf4 ? 256 : 128;
+    const uint32_t half_k = mxf4 ? 256 : 128;     // K elements of one 128-byte slab
     const uint32_t sms = d->num_sms ? d->num_sms : 148;
     const uint32_t groups = d->num_groups ? d->num_groups : 1;
-    const uint32_t sfa_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
-    const uint32_t sfb_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
     const uint32_t step = d->cd_dtype == DG_OUT_FP8 ? 128 : 32;
     const uint32_t align = g_mk_alignment.load();
     const char* force_n = getenv("DG_BLOCK_N");
@@ -190,8 +188,15 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
     const char* force_stages = getenv("DG_STAGES");
 
     const char* force_splits = getenv("DG_SPLITS");
-    uint32_t best_n = 0, best_accum = 0, best_tiles = 0, best_ctas = 0, best_stages = 0, best_splits = 1;
+    const char* force_halves = getenv("DG_K_SLABS");
+    uint32_t best_n = 0, best_accum = 0, best_tiles = 0, best_ctas = 0, best_stages = 0, best_splits = 1, best_halves = 1;
     double best_cost = 0;
+    // a stage holds one or two 128-byte K slabs per operand; two slabs halve the per-stage bookkeeping per UMMA
+    for (uint32_t halves = 1; halves <= 2; ++halves) {
+    if (force_halves && static_cast<uint32_t>(atoi(force_halves)) != halves) continue;
+    const uint32_t block_k = half_k * halves;
+    const uint32_t sfa_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
+    const uint32_t sfb_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
     for (uint32_t ctas = 1; ctas <= 2; ++ctas) {
         if (force_ctas && static_cast<uint32_t>(atoi(force_ctas)) != ctas) continue;
         const uint32_t tile_m = 128 * ctas;
@@ -223,12 +228,12 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
             const double mma = 4.0 * (bn * 0.5 > 118.0 ? bn * 0.5 : 118.0);
             const double feed = (16384.0 + bn / ctas * 128.0) / 77.0;
             const double epilogue = accum == 1 ? 10.5 * bn : 1.0 * bn;
-            const double per_kb = (mma > feed ? mma : feed) + 150.0;
+            const double per_kb = halves * (mma > feed ? mma : feed) + 150.0;
             // K ranges (dense GEMMs with f32-summable outputs only): each range is a multiple of 4 k-blocks so scale words
             // never straddle ranges; the partial sums cost a second small kernel (launch + S reads of the M x N f32 tile set)
             const bool may_split = d->gemm_type == DG_GEMM_NORMAL && d->cd_dtype != DG_OUT_FP8 && d->n % 4 == 0;
             for (uint32_t splits = 1; splits <= 16; ++splits) {
-                if (splits > 1 && !may_split) break;
+                if (splits > 1 && (!may_split || halves > 1)) break;
                 if (force_splits && static_cast<uint32_t>(atoi(force_splits)) != splits) continue;
                 uint32_t kb_per = ceil_div(ceil_div(total_kb, splits), 4) * 4;
                 if (splits > 1 && (kb_per < 8 || kb_per * (splits - 1) >= total_kb)) continue;   // every range non-empty, at least 8 k-blocks
@@ -237,8 +242,8 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
                 const uint32_t kernel_out = splits > 1 ? static_cast<uint32_t>(DG_OUT_F32) : d->cd_dtype;
                 uint32_t stages = force_stages ? static_cast<uint32_t>(atoi(force_stages)) : dg::kMaxStages;
                 if (stages > dg::kMaxStages) stages = dg::kMaxStages;
-                while (stages > 1 && dg::gemm_smem_bytes(bn, ctas, kernel_out, stages, sfa_words, sfb_words) > kSmemCapacity) --stages;
-                if (stages < 1 || dg::gemm_smem_bytes(bn, ctas, kernel_out, stages, sfa_words, sfb_words) > kSmemCapacity) continue;
+                while (stages > 1 && dg::gemm_smem_bytes(bn, ctas, kernel_out, stages, sfa_words, sfb_words, halves) > kSmemCapacity) --stages;
+                if (stages < 1 || dg::gemm_smem_bytes(bn, ctas, kernel_out, stages, sfa_words, sfb_words, halves) > kSmemCapacity) continue;
                 if (stages < 3 && !force_stages) continue;
                 const uint32_t waves = ceil_div(tiles * splits, workers);
                 const double tile_cost = kb_per * per_kb + (splits > 1 ? 2.0 * bn : epilogue) + 600.0;
@@ -246,22 +251,27 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
                 const double cost = waves * tile_cost + reduce;
                 if (best_n == 0 || cost < best_cost * (1.0 - 1e-9)) {
                     best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; best_ctas = ctas; best_stages = stages;
-                    best_splits = splits;
+                    best_splits = splits; best_halves = halves;
                 }
             }
         }
+    }
     }
     if (best_n == 0) return fail(DG_ERR_SHAPE, "no tile configuration fits (DG_BLOCK_N=%s DG_CTAS=%s)", force_n ? force_n : "", force_ctas ? force_ctas : "");
     const uint32_t stages = best_stages;
     out->swap_ab = 0;
     out->block_m = 128 * best_ctas;
     out->block_n = best_n;
+    const uint32_t block_k = half_k * best_halves;
+    const uint32_t sfa_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
+    const uint32_t sfb_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
     out->block_k = block_k;
     out->cluster_m = best_ctas;
     out->cluster_n = 1;
     out->num_stages = stages;
     out->num_accum_stages = best_accum;
-    out->smem_size = dg::gemm_smem_bytes(best_n, best_ctas, best_splits > 1 ? static_cast<uint32_t>(DG_OUT_F32) : d->cd_dtype, stages, sfa_words, sfb_words);
+    out->smem_size = dg::gemm_smem_bytes(best_n, best_ctas, best_splits > 1 ? static_cast<uint32_t>(DG_OUT_F32) : d->cd_dtype, stages, sfa_words,
+                                         sfb_words, best_halves);
     out->num_tiles = best_tiles;
     out->num_splits = best_splits;
     return DG_OK;
@@ -415,12 +425,13 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         const uint64_t a_pitch = mxf4 ? a->ld / 2 : a->ld, b_pitch = mxf4 ? b->ld / 2 : b->ld;
         uint64_t dims[3] = {pr.k, pr.m, a_groups};
         uint64_t strides[2] = {a_pitch, a_pitch * pr.m};
-        uint32_t box[3] = {block_k, dg::kBlockM, 1};
+        const uint32_t slab = mxf4 ? 256u : 128u;    // one 128-byte slab of K per TMA box
+        uint32_t box[3] = {slab, dg::kBlockM, 1};
         rc = encode_map(&maps[0], dt, 3, a->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
         if (rc) return rc;
         uint64_t bdims[3] = {pr.k, pr.n, b_groups};
         uint64_t bstrides[2] = {b_pitch, b_pitch * pr.n};
-        uint32_t bbox[3] = {block_k, cfg.block_n / cfg.cluster_m, 1};
+        uint32_t bbox[3] = {slab, cfg.block_n / cfg.cluster_m, 1};
         rc = encode_map(&maps[1], dt, 3, b->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
         if (rc) return rc;
     }

@@ -31,7 +31,7 @@ enum GemmType : uint32_t { kGemmNormal = 0, kGemmContiguous = 1, kGemmMasked = 2
 enum OutKind : uint32_t { kOutBf16 = 0, kOutF32 = 1, kOutFp8 = 2 };
 
 constexpr uint32_t kBlockM = 128;          // UMMA M, rows of A per tile
-constexpr uint32_t kBlockKBytes = 128;     // one 128-byte swizzle row of K per stage
+constexpr uint32_t kBlockKBytes = 128;     // one 128-byte swizzle row of K per TMA box / UMMA group ("half" of a double stage)
 constexpr uint32_t kUmmaKBytes = 32;       // K bytes consumed by one UMMA
 constexpr uint32_t kMaxStages = 12;
 constexpr uint32_t kNumThreads = 256;
@@ -193,7 +193,11 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                const __grid_constant__ CUtensorMap tmap_d) {
-    constexpr uint32_t kBlockKElems = kMXF4 ? 256 : 128;
+    // a stage holds one or two 128-byte K slabs per operand (block_k_elems = halves x 128 e4m3 / 256 e2m1):
+    // two slabs halve the per-stage bookkeeping (waits, commits) the UMMA warp does per UMMA
+    constexpr uint32_t kHalfElems = kMXF4 ? 256 : 128;
+    const uint32_t kBlockKElems = p.block_k_elems;
+    const uint32_t halves = kBlockKElems / kHalfElems;
     constexpr uint32_t kEpiBufBytes = epilogue_buf_bytes(kOut);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -207,7 +211,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
     const SfPlan plan_a = sf_plan(p.gran_a, kBlockKElems), plan_b = sf_plan(p.gran_b, kBlockKElems);
     const uint32_t sfa_bytes = 512 * plan_a.words, sfb_bytes = sf_block_n * 4 * plan_b.words;
-    const uint32_t a_bytes = kBlockM * kBlockKBytes, b_bytes = load_n * kBlockKBytes;
+    const uint32_t a_half = kBlockM * kBlockKBytes, b_half = load_n * kBlockKBytes;
+    const uint32_t a_bytes = a_half * halves, b_bytes = b_half * halves;
     const uint32_t num_stages = p.num_stages;
 
     // shared memory carve-up (every tile base stays 1024-byte aligned)
@@ -286,17 +291,21 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                             tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0),
                                         static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words));
                     }
-                    const int32_t kx = static_cast<int32_t>(kb * kBlockKElems);
-                    if constexpr (kCtas == 1) {
-                        mbar_arrive_expect_tx(bar_full + stage, a_bytes + b_bytes);
-                        tma_load_3d(smem_a + stage * a_bytes, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
-                        tma_load_3d(smem_b + stage * b_bytes, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
-                    } else {
-                        // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
-                        if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * (a_bytes + b_bytes));
-                        const uint32_t bar_addr = full_bar_leader + stage * 8;
-                        tma_load_3d_2cta(smem_a + stage * a_bytes, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
-                        tma_load_3d_2cta(smem_b + stage * b_bytes, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
+                    if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, a_bytes + b_bytes);
+                    // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
+                    else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * (a_bytes + b_bytes));
+                    for (uint32_t h = 0; h < halves; ++h) {
+                        const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
+                        uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
+                        uint8_t* dst_b = smem_b + stage * b_bytes + h * b_half;
+                        if constexpr (kCtas == 1) {
+                            tma_load_3d(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
+                            tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
+                        } else {
+                            const uint32_t bar_addr = full_bar_leader + stage * 8;
+                            tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
+                            tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
+                        }
                     }
                 }
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
@@ -341,35 +350,44 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     DG_PROF_T(t_issue);
                     tc_fence_after();
                     const uint32_t sfa_addr = smem_u32(smem_sfa + stage * sfa_bytes), sfb_addr = smem_u32(smem_sfb + stage * sfb_bytes);
-                    const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes), 0, 1024, 2);
-                    const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes), 0, 1024, 2);
-                    // everything the issuing lane needs is computed here, outside the single-lane region
-                    uint32_t idescs[4], a_cols[4], b_cols[4];
-                    #pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k) {
-                        uint32_t a_id, b_id;
-                        if constexpr (kMXF4) {
-                            // one UMMA spans 64 elements = two scale bytes; a word spans two UMMAs
-                            a_id = (k & 1) * 2; b_id = (k & 1) * 2;
-                            a_cols[k] = tmem_sfa + 4 * (k / 2); b_cols[k] = tmem_sfb + 4 * (k / 2) * (sf_block_n / 128);
-                        } else {
-                            a_id = p.gran_a == 128 ? kb % 4 : k;
-                            b_id = p.gran_b == 128 ? kb % 4 : k;
-                            a_cols[k] = tmem_sfa; b_cols[k] = tmem_sfb;
-                        }
-                        idescs[k] = idesc_with_sf_ids(idesc, a_id, b_id);
-                    }
                     const uint64_t sfa_desc = make_smem_desc(sfa_addr, 0, 128, 0), sfb_desc = make_smem_desc(sfb_addr, 0, 128, 0);
                     const bool last = kb + 1 == t.kb1;
-                    if (elect_one()) {
+                    const bool leader_lane = elect_one();
+                    if (leader_lane) {
                         if (need_a)
                             for (uint32_t c = 0; c < plan_a.words; ++c) utccp_32x128b_warpx4<kCtas>(tmem_sfa + 4 * c, sfa_desc + c * (512 >> 4));
                         if (need_b)
                             for (uint32_t c = 0; c < chunks_b; ++c) utccp_32x128b_warpx4<kCtas>(tmem_sfb + 4 * c, sfb_desc + c * (512 >> 4));
+                    }
+                    for (uint32_t h = 0; h < halves; ++h) {
+                        // everything the issuing lane needs is computed here, outside the single-lane region
+                        uint32_t idescs[4], a_cols[4], b_cols[4];
                         #pragma unroll
-                        for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
-                            umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
-                                                            a_cols[k], b_cols[k], (kb != t.kb0 || k != 0) ? 1u : 0u);
+                        for (uint32_t k = 0; k < 4; ++k) {
+                            uint32_t a_id, b_id;
+                            if constexpr (kMXF4) {
+                                // one UMMA spans 64 elements = two scale bytes; a word spans two UMMAs, a slab two words
+                                a_id = (k & 1) * 2; b_id = (k & 1) * 2;
+                                a_cols[k] = tmem_sfa + 4 * (h * 2 + k / 2); b_cols[k] = tmem_sfb + 4 * (h * 2 + k / 2) * (sf_block_n / 128);
+                            } else {
+                                // per-128 scales: one byte per slab, four slabs per word; per-32 scales: one word per slab
+                                a_id = p.gran_a == 128 ? (kb * halves + h) % 4 : k;
+                                b_id = p.gran_b == 128 ? (kb * halves + h) % 4 : k;
+                                a_cols[k] = tmem_sfa + (p.gran_a == 128 ? 0u : 4 * h);
+                                b_cols[k] = tmem_sfb + (p.gran_b == 128 ? 0u : 4 * h * (sf_block_n / 128));
+                            }
+                            idescs[k] = idesc_with_sf_ids(idesc, a_id, b_id);
+                        }
+                        const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes + h * a_half), 0, 1024, 2);
+                        const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes + h * b_half), 0, 1024, 2);
+                        if (leader_lane) {
+                            #pragma unroll
+                            for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
+                                umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
+                                                                a_cols[k], b_cols[k], (kb != t.kb0 || h != 0 || k != 0) ? 1u : 0u);
+                        }
+                    }
+                    if (leader_lane) {
                         if constexpr (kCtas == 1) {
                             umma_commit(bar_empty + stage);
                             if (last) umma_commit(bar_tmem_full + e);
@@ -560,9 +578,10 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 }
 
 // Bytes of dynamic shared memory the kernel needs for a configuration (host side).
-inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t ctas, uint32_t out_kind, uint32_t stages, uint32_t sfa_words, uint32_t sfb_words) {
+inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t ctas, uint32_t out_kind, uint32_t stages, uint32_t sfa_words, uint32_t sfb_words,
+                                uint32_t halves) {
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
-    const uint32_t per_stage = kBlockM * kBlockKBytes + block_n / ctas * kBlockKBytes + 512 * sfa_words + sf_block_n * 4 * sfb_words;
+    const uint32_t per_stage = halves * (kBlockM * kBlockKBytes + block_n / ctas * kBlockKBytes) + 512 * sfa_words + sf_block_n * 4 * sfb_words;
     return 1024 + stages * per_stage + 8 * epilogue_buf_bytes(out_kind) + (4 * kMaxStages + 4) * 8 + 16;
 }
 

@@ -78,7 +78,8 @@ def test_dense_fp8_small(ctx, m, n, k):
 
 @pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("block_n", [32, 64, 96, 128, 160, 192, 224, 256])
-def test_dense_fp8_every_tile_shape(ctx, ctas, block_n, monkeypatch):
+@pytest.mark.parametrize("slabs", [1, 2])
+def test_dense_fp8_every_tile_shape(ctx, ctas, block_n, slabs, monkeypatch):
     # DG_BLOCK_N / DG_CTAS pin the tile the heuristic would otherwise choose: every width the epilogue can
     # store, single CTA and CTA pair (256-row tiles, B split between the two CTAs), single- and
     # double-buffered accumulators, with ragged M and N so edge tiles are partly out of bounds
@@ -86,9 +87,17 @@ def test_dense_fp8_every_tile_shape(ctx, ctas, block_n, monkeypatch):
         pytest.skip("tile width not issuable")
     monkeypatch.setenv("DG_BLOCK_N", str(block_n))
     monkeypatch.setenv("DG_CTAS", str(ctas))
-    cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 600, 1000, 1152))
-    assert cfg.block_n == block_n and cfg.cluster_m == ctas and cfg.block_m == 128 * ctas
+    monkeypatch.setenv("DG_K_SLABS", str(slabs))     # 128 or 256 bytes of K per pipeline stage (K = 1152 leaves a half-empty last stage)
+    try:
+        cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 600, 1000, 1152))
+    except dg.DgError:
+        pytest.skip("this tile does not fit three stages of two slabs")
+    assert cfg.block_n == block_n and cfg.cluster_m == ctas and cfg.block_m == 128 * ctas and cfg.block_k == 128 * slabs
     run_dense(ctx, 600, 1000, 1152, seed=block_n + ctas)
+    try:
+        dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 600, 1000, 1152, cd_dtype=1))
+    except dg.DgError:
+        return                                       # the wider f32 staging buffers leave too few stages for this tile
     run_dense(ctx, 600, 1000, 1152, out_kind=1, seed=block_n + ctas)
 
 
