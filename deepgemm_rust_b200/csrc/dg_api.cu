@@ -204,14 +204,20 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
         // never stored (groups start on multiples of 128, stores are 32 rows tall), so any 128-multiple alignment works
         if (ctas == 2 && d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS && align % 128 != 0) continue;
         if (ctas == 2 && sms < 2) continue;
-        uint32_t m_blocks;
+        // expected row-tiles.  Grouped layouts: a group of r valid rows needs ceil(r / tile_m) tiles, on average
+        // r / tile_m + 1/2 when group sizes are spread out; the contiguous arena's m includes about half an alignment of
+        // padding per group.
+        double m_blocks;
         if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) {
-            // groups are padded to the alignment and every group rounds up to whole tiles
-            const uint32_t per_group = groups ? d->m / groups : d->m;
-            m_blocks = groups * ceil_div(per_group ? per_group : 1, tile_m);
+            const double per_group = groups ? static_cast<double>(d->m) / groups : d->m;
+            const double valid = per_group > align / 2.0 ? per_group - align / 2.0 : per_group;
+            m_blocks = groups > 1 ? groups * (valid / tile_m + 0.5) : ceil_div(d->m, tile_m);
+        } else if (d->gemm_type == DG_GEMM_M_GROUPED_MASKED) {
+            const double e = d->expected_m ? d->expected_m : d->m;
+            m_blocks = groups * (e / tile_m + 0.5);
+        } else {
+            m_blocks = groups * ceil_div(d->m, tile_m);
         }
-        else if (d->gemm_type == DG_GEMM_M_GROUPED_MASKED) m_blocks = groups * ceil_div(d->expected_m ? d->expected_m : d->m, tile_m);
-        else m_blocks = groups * ceil_div(d->m, tile_m);
         const uint32_t workers = sms / ctas;
         for (uint32_t bn = step; bn <= 256; bn += step) {
             if (bn % (16 * ctas) != 0) continue;
@@ -219,7 +225,7 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
             const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
             if (bn + sf_cols > 512) continue;
             const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
-            const uint32_t tiles = m_blocks * ceil_div(d->n, bn);
+            const uint32_t tiles = static_cast<uint32_t>(m_blocks * ceil_div(d->n, bn) + 0.999);
             // cycles per tile, fitted to measurements on B200 (dense 4096x7168x4096, every width, 1 and 2 CTAs):
             // per k-block max(UMMA time, load time) + ~150 of issue-side overhead, where one UMMA (K = 32 bytes) takes
             // max(~118, bn / 2) cycles and a CTA receives its A tile (16 KB) plus bn/ctas rows of B at ~77 bytes per cycle;
@@ -248,7 +254,12 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
                 const uint32_t waves = ceil_div(tiles * splits, workers);
                 const double tile_cost = kb_per * per_kb + (splits > 1 ? 2.0 * bn : epilogue) + 600.0;
                 const double reduce = splits > 1 ? 9000.0 + static_cast<double>(splits) * d->m * d->n * 4.0 / 3000.0 : 0.0;
-                const double cost = waves * tile_cost + reduce;
+                // every CTA pulls its A slab (16 KB) and its share of B from L2 for each 128 bytes of K; with many small groups
+                // (weights read once, little reuse) that aggregate stream, ~9000 bytes per cycle on this part, is the limit
+                const double l2_bytes = static_cast<double>(tiles) * ctas * ceil_div(d->k, half_k) * (16384.0 + bn / ctas * 128.0);
+                const double l2_floor = l2_bytes / 9000.0;
+                const double compute = waves * tile_cost;
+                const double cost = (compute > l2_floor ? compute : l2_floor) + reduce;
                 if (best_n == 0 || cost < best_cost * (1.0 - 1e-9)) {
                     best_n = bn; best_cost = cost; best_accum = accum; best_tiles = tiles; best_ctas = ctas; best_stages = stages;
                     best_splits = splits; best_halves = halves;
