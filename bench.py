@@ -323,12 +323,15 @@ def main():
     ap.add_argument("--workload", default=None, help="dense_fp8 (default at 1 GPU) or moe_ep (default at more)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--moe-experts", type=int, default=None, help="moe_ep: total experts (default 256); 32 gives one rank of an 8-GPU job")
     ap.add_argument("--only", default=None, help="M,N,K: restrict the dense pass to one GEMM (profiling captures)")
     args = ap.parse_args()
     if args.only:
         global DENSE_SHAPES, DOMINANT
         DOMINANT = tuple(int(x) for x in args.only.split(","))
         DENSE_SHAPES = [DOMINANT]
+    if args.moe_experts:
+        MOE["experts"] = args.moe_experts
     if args.impl == "reference":
         run_reference(args)
         return
@@ -490,7 +493,7 @@ def main():
                     "frac": achieved / peak if achieved else None,
                     # dram__bytes_read.sum + dram__bytes_write.sum of this launch, one ncu capture
                     # (profiles/dg_gemm_kernel_fp8_M4096_N7168_K16384.md); algorithmic bytes are 2.447e8
-                    "traffic": 6.384e8 if DOMINANT == (4096, 7168, 16384) else None,
+                    "traffic": 6.48e8 if DOMINANT == (4096, 7168, 16384) else None,
                     "kernel": "dg_gemm_kernel<fp8, bf16 out>", "launch": f"M={m} N={n} K={k}",
                     "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} peaks (e4m3 issues at twice the bf16 rate)",
                     "frac_of_nominal_fp8_4500": achieved / 4500.0 if achieved else None}

@@ -129,6 +129,10 @@ class ExpertParallel:
 
     def combine(self, plan: Plan, y: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """Arena result rows (m_pad, n) bf16 -> per-token weighted sums (tokens, n) on the token ranks."""
+        if not self.distributed:
+            # one rank: result rows never leave; reduce straight from the arena through the composed index
+            arena_pos = plan.dst_pos[plan.pos_of_pair.reshape(-1).long()].reshape(plan.tokens, plan.topk).contiguous()
+            return self.ops.combine(y, arena_pos, weights)
         back = self.ops.gather(y, plan.dst_pos, plan.n_recv)
         home = self._exchange(back, plan.pairs, plan.send_splits, plan.recv_splits)
         return self.ops.combine(home, plan.pos_of_pair, weights)
