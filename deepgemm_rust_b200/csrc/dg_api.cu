@@ -685,7 +685,7 @@ static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32
     p.sf_cols = dg_sf_packed_cols(k, gran);
     p.sf_stride = align4(rows / groups);
     p.rule = rule;
-    const uint64_t units = static_cast<uint64_t>(rows) * ceil_div(k, 512);
+    const uint64_t units = static_cast<uint64_t>(rows) * ceil_div(k, 1024);   // one warp per 1024-element row segment
     const uint32_t blocks = static_cast<uint32_t>((units + 7) / 8);
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     if (fp4) dg::dg_cast_kernel<32, true><<<blocks, 256, 0, ctx->stream>>>(p);

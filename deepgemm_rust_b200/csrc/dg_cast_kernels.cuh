@@ -1,7 +1,7 @@
 // Memory-bound kernels either side of the GEMM: bf16 -> e4m3 / e2m1 quantisation with packed
 // UE8M0 scale factors, f32 scale-factor re-layouts, and the group-end table of the contiguous
 // MoE layout.  All of them are HBM-bound byte/integer work: 16-byte loads and stores, one warp
-// per 512-element row segment, scale words written straight into the packed layout
+// per 1024-element row segment, scale words written straight into the packed layout
 //   word(group g, local row r, column c) = sf[(g * cols + c) * align4(group_rows) + r],
 //   byte j of a word = exponent of K block 4c + j.
 #pragma once
@@ -38,29 +38,30 @@ struct CastParams {
     int rule;
 };
 
-// One warp quantises 512 consecutive K elements of one row: two 16-byte loads per lane
-// (elements [8*lane, +8) and [256 + 8*lane, +8)).  kGran = 128: 16 lanes share a scale, the
-// warp produces one scale word.  kGran = 32: 4 lanes share a scale, the warp produces 4 words.
+// One warp quantises 1024 consecutive K elements of one row: four 16-byte loads per lane, all issued
+// before the first use (elements [256*h + 8*lane, +8) for h = 0..3).  kGran = 128: 16 lanes share a scale,
+// the warp produces two scale words.  kGran = 32: 4 lanes share a scale, the warp produces 8 words.
 template <uint32_t kGran, bool kFp4>
 __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
+    constexpr uint32_t kLoads = 4, kSeg = 256 * kLoads;
     const uint32_t lane = threadIdx.x % 32;
-    const uint32_t segs_per_row = (p.k + 511) / 512;
+    const uint32_t segs_per_row = (p.k + kSeg - 1) / kSeg;
     const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
     if (unit >= static_cast<uint64_t>(p.rows) * segs_per_row) return;
     const uint32_t row = static_cast<uint32_t>(unit / segs_per_row), seg = static_cast<uint32_t>(unit % segs_per_row);
     const uint32_t group = row / p.group_rows, local_row = row - group * p.group_rows;
     const uint16_t* src_row = p.src + static_cast<size_t>(row) * p.src_ld;
 
-    uint4 raw[2];
-    uint32_t k0[2];
+    uint4 raw[kLoads];
+    uint32_t k0[kLoads];
     #pragma unroll
-    for (uint32_t h = 0; h < 2; ++h) {
-        k0[h] = seg * 512 + h * 256 + lane * 8;
+    for (uint32_t h = 0; h < kLoads; ++h) {
+        k0[h] = seg * kSeg + h * 256 + lane * 8;
         raw[h] = k0[h] < p.k ? __ldg(reinterpret_cast<const uint4*>(src_row + k0[h])) : make_uint4(0, 0, 0, 0);
     }
-    uint32_t exps[2];
+    uint32_t exps[kLoads];
     #pragma unroll
-    for (uint32_t h = 0; h < 2; ++h) {
+    for (uint32_t h = 0; h < kLoads; ++h) {
         float v[8] = {bf16_lo(raw[h].x), bf16_hi(raw[h].x), bf16_lo(raw[h].y), bf16_hi(raw[h].y),
                       bf16_lo(raw[h].z), bf16_hi(raw[h].z), bf16_lo(raw[h].w), bf16_hi(raw[h].w)};
         float amax = 0.0f;
@@ -92,34 +93,38 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
             }
         }
     }
-    // assemble scale words: exps[h] on lane l belongs to K block (seg*512 + h*256 + l*8) / kGran
+    // assemble scale words: exps[h] on lane l belongs to K block (seg*1024 + h*256 + l*8) / kGran
     if constexpr (kGran == 128) {
-        const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, exps[0], 0), e1 = __shfl_sync(0xFFFFFFFFu, exps[0], 16);
-        const uint32_t e2 = __shfl_sync(0xFFFFFFFFu, exps[1], 0), e3 = __shfl_sync(0xFFFFFFFFu, exps[1], 16);
-        if (lane == 0) {
-            const uint32_t blocks = (p.k + 127) / 128, b0 = seg * 4;
-            uint32_t w = e0;
-            if (b0 + 1 < blocks) w |= e1 << 8;
-            if (b0 + 2 < blocks) w |= e2 << 16;
-            if (b0 + 3 < blocks) w |= e3 << 24;
-            p.sf[(static_cast<size_t>(group) * p.sf_cols + seg) * p.sf_stride + local_row] = w;
+        // word w of this segment covers loads 2w and 2w+1 (two 128-element blocks each)
+        #pragma unroll
+        for (uint32_t w = 0; w < kLoads / 2; ++w) {
+            const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, exps[2 * w], 0), e1 = __shfl_sync(0xFFFFFFFFu, exps[2 * w], 16);
+            const uint32_t e2 = __shfl_sync(0xFFFFFFFFu, exps[2 * w + 1], 0), e3 = __shfl_sync(0xFFFFFFFFu, exps[2 * w + 1], 16);
+            const uint32_t col = seg * (kLoads / 2) + w;
+            if (lane == w && col * 512 < p.k) {
+                const uint32_t blocks = (p.k + 127) / 128, b0 = col * 4;
+                uint32_t word = e0;
+                if (b0 + 1 < blocks) word |= e1 << 8;
+                if (b0 + 2 < blocks) word |= e2 << 16;
+                if (b0 + 3 < blocks) word |= e3 << 24;
+                p.sf[(static_cast<size_t>(group) * p.sf_cols + col) * p.sf_stride + local_row] = word;
+            }
         }
     } else {
-        // word c of this segment (c = 0..3) covers elements [c*128, +128): lanes 16*(c%2).. of half c/2
+        // word c of this segment (c = 0..7) covers elements [c*128, +128): lanes 16*(c%2).. of load c/2
         #pragma unroll
-        for (uint32_t c = 0; c < 4; ++c) {
-            const uint32_t h = c / 2, base = (c % 2) * 16;
-            const uint32_t src_exp = h == 0 ? exps[0] : exps[1];
+        for (uint32_t c = 0; c < 2 * kLoads; ++c) {
+            const uint32_t src_exp = exps[c / 2], base = (c % 2) * 16;
             const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, src_exp, base), b1 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 4);
             const uint32_t b2 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 8), b3 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 12);
-            const uint32_t col = seg * 4 + c;
+            const uint32_t col = seg * 2 * kLoads + c;
             if (lane == c && col * 128 < p.k) {
                 const uint32_t blocks = (p.k + 31) / 32, first = col * 4;
-                uint32_t w = b0;
-                if (first + 1 < blocks) w |= b1 << 8;
-                if (first + 2 < blocks) w |= b2 << 16;
-                if (first + 3 < blocks) w |= b3 << 24;
-                p.sf[(static_cast<size_t>(group) * p.sf_cols + col) * p.sf_stride + local_row] = w;
+                uint32_t word = b0;
+                if (first + 1 < blocks) word |= b1 << 8;
+                if (first + 2 < blocks) word |= b2 << 16;
+                if (first + 3 < blocks) word |= b3 << 24;
+                p.sf[(static_cast<size_t>(group) * p.sf_cols + col) * p.sf_stride + local_row] = word;
             }
         }
     }
