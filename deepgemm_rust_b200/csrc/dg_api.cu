@@ -685,8 +685,10 @@ static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32
     p.sf_cols = dg_sf_packed_cols(k, gran);
     p.sf_stride = align4(rows / groups);
     p.rule = rule;
-    const uint64_t units = static_cast<uint64_t>(rows) * ceil_div(k, 1024);   // one warp per 1024-element row segment
-    const uint32_t blocks = static_cast<uint32_t>((units + 7) / 8);
+    // one block per 8 consecutive rows x one 1024-element segment (one warp per row)
+    const uint64_t units = static_cast<uint64_t>(ceil_div(rows, 8)) * ceil_div(k, 1024);
+    if (units > 0x7FFFFFFFull) return fail(DG_ERR_SHAPE, "matrix too large for one launch");
+    const uint32_t blocks = static_cast<uint32_t>(units);
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     if (fp4) dg::dg_cast_kernel<32, true><<<blocks, 256, 0, ctx->stream>>>(p);
     else if (gran == 32) dg::dg_cast_kernel<32, false><<<blocks, 256, 0, ctx->stream>>>(p);

@@ -44,20 +44,23 @@ struct CastParams {
 template <uint32_t kGran, bool kFp4>
 __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
     constexpr uint32_t kLoads = 4, kSeg = 256 * kLoads;
-    const uint32_t lane = threadIdx.x % 32;
+    // a block takes 8 consecutive rows (one per warp) of one segment, so that the scale words of a word column,
+    // which are contiguous over rows, leave the block as whole 32-byte sectors
+    constexpr uint32_t kWordsPerWarp = kGran == 128 ? kLoads / 2 : 2 * kLoads;
+    __shared__ uint32_t words[kWordsPerWarp][8];
+    const uint32_t lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const uint32_t segs_per_row = (p.k + kSeg - 1) / kSeg;
-    const uint64_t unit = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
-    if (unit >= static_cast<uint64_t>(p.rows) * segs_per_row) return;
-    const uint32_t row = static_cast<uint32_t>(unit / segs_per_row), seg = static_cast<uint32_t>(unit % segs_per_row);
-    const uint32_t group = row / p.group_rows, local_row = row - group * p.group_rows;
-    const uint16_t* src_row = p.src + static_cast<size_t>(row) * p.src_ld;
+    const uint32_t seg = blockIdx.x % segs_per_row, row0 = (blockIdx.x / segs_per_row) * 8;
+    const uint32_t row = row0 + warp;
+    const bool live = row < p.rows;
+    const uint16_t* src_row = p.src + static_cast<size_t>(live ? row : 0) * p.src_ld;
 
     uint4 raw[kLoads];
     uint32_t k0[kLoads];
     #pragma unroll
     for (uint32_t h = 0; h < kLoads; ++h) {
         k0[h] = seg * kSeg + h * 256 + lane * 8;
-        raw[h] = k0[h] < p.k ? __ldg(reinterpret_cast<const uint4*>(src_row + k0[h])) : make_uint4(0, 0, 0, 0);
+        raw[h] = (live && k0[h] < p.k) ? __ldg(reinterpret_cast<const uint4*>(src_row + k0[h])) : make_uint4(0, 0, 0, 0);
     }
     uint32_t exps[kLoads];
     #pragma unroll
@@ -79,7 +82,7 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
             inv = __uint_as_float((254u - e) << 23);
         }
         exps[h] = e;
-        if (k0[h] < p.k) {
+        if (live && k0[h] < p.k) {
             if constexpr (kFp4) {
                 float s[8];
                 #pragma unroll
@@ -101,13 +104,13 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
             const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, exps[2 * w], 0), e1 = __shfl_sync(0xFFFFFFFFu, exps[2 * w], 16);
             const uint32_t e2 = __shfl_sync(0xFFFFFFFFu, exps[2 * w + 1], 0), e3 = __shfl_sync(0xFFFFFFFFu, exps[2 * w + 1], 16);
             const uint32_t col = seg * (kLoads / 2) + w;
-            if (lane == w && col * 512 < p.k) {
+            if (lane == w) {
                 const uint32_t blocks = (p.k + 127) / 128, b0 = col * 4;
                 uint32_t word = e0;
                 if (b0 + 1 < blocks) word |= e1 << 8;
                 if (b0 + 2 < blocks) word |= e2 << 16;
                 if (b0 + 3 < blocks) word |= e3 << 24;
-                p.sf[(static_cast<size_t>(group) * p.sf_cols + col) * p.sf_stride + local_row] = word;
+                words[w][warp] = word;
             }
         }
     } else {
@@ -118,14 +121,24 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
             const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, src_exp, base), b1 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 4);
             const uint32_t b2 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 8), b3 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 12);
             const uint32_t col = seg * 2 * kLoads + c;
-            if (lane == c && col * 128 < p.k) {
+            if (lane == c) {
                 const uint32_t blocks = (p.k + 31) / 32, first = col * 4;
                 uint32_t word = b0;
                 if (first + 1 < blocks) word |= b1 << 8;
                 if (first + 2 < blocks) word |= b2 << 16;
                 if (first + 3 < blocks) word |= b3 << 24;
-                p.sf[(static_cast<size_t>(group) * p.sf_cols + col) * p.sf_stride + local_row] = word;
+                words[c][warp] = word;
             }
+        }
+    }
+    __syncthreads();
+    // thread t writes word column t / 8 of row t % 8: eight consecutive rows of a column are 32 contiguous bytes
+    if (threadIdx.x < kWordsPerWarp * 8) {
+        const uint32_t c = threadIdx.x / 8, r = row0 + threadIdx.x % 8;
+        const uint32_t col = seg * kWordsPerWarp + c;
+        if (r < p.rows && col < p.sf_cols) {
+            const uint32_t g = r / p.group_rows, lr = r - g * p.group_rows;
+            p.sf[(static_cast<size_t>(g) * p.sf_cols + col) * p.sf_stride + lr] = words[c][threadIdx.x % 8];
         }
     }
 }
