@@ -176,8 +176,9 @@ uint32_t dg_get_theoretical_mk_alignment_for_contiguous_layout(uint32_t arch_maj
 int dg_best_config(const dg_desc* d, dg_config* out) {
     if (d == nullptr || out == nullptr) return fail(DG_ERR_SHAPE, "null argument");
     if ((d->a_bits != 8 && d->a_bits != 4) || (d->b_bits != 8 && d->b_bits != 4)) return fail(DG_ERR_SHAPE, "operand bits must be 8 or 4");
-    if (d->a_bits != d->b_bits) return fail(DG_ERR_UNSUPPORTED, "mixed FP8 x FP4 operands are not built yet");
-    const bool mxf4 = d->a_bits == 4;
+    // two packed e2m1 operands run on kind::mxf4 (256 elements per 128-byte slab); an e4m3 x e2m1 pair runs on
+    // kind::mxf8f6f4 with the e2m1 side expanded to one code per byte by the TMA load (128 elements per slab)
+    const bool mxf4 = d->a_bits == 4 && d->b_bits == 4;
     const uint32_t half_k = mxf4 ? 256 : 128;     // K elements of one 128-byte slab
     const uint32_t sms = d->num_sms ? d->num_sms : 148;
     const uint32_t groups = d->num_groups ? d->num_groups : 1;
@@ -379,7 +380,6 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     if (e.accumulate && e.has_alpha) return fail(DG_ERR_SHAPE, "alpha and accumulation are mutually exclusive");
     if (e.accumulate) return fail(DG_ERR_UNSUPPORTED, "accumulation into the output is not built yet");
     if (a->k != b->k) return fail(DG_ERR_SHAPE, "a.k (%u) != b.k (%u)", a->k, b->k);
-    if (a->bits != b->bits) return fail(DG_ERR_UNSUPPORTED, "mixed FP8 x FP4 operands are not built yet");
     if (pr.m == 0 || pr.n == 0) return DG_OK;
     const bool contiguous = pr.type == DG_GEMM_M_GROUPED_CONTIGUOUS;
     const uint32_t a_groups = contiguous || pr.type == DG_GEMM_NORMAL ? 1 : pr.groups;
@@ -413,7 +413,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
                 pr.n, pr.k, pr.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_m, cfg.num_stages, cfg.num_accum_stages, cfg.smem_size,
                 cfg.num_tiles);
 
-    const bool mxf4 = a->bits == 4;
+    const bool mxf4 = a->bits == 4 && b->bits == 4;
     const uint32_t block_k = cfg.block_k;
     const uint32_t splits = cfg.num_splits;
     const uint32_t ws_pitch = align4(pr.n);
@@ -432,18 +432,22 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
 
     CUtensorMap maps[5];
     {
-        const CUtensorMapDataType dt = mxf4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-        const uint64_t a_pitch = mxf4 ? a->ld / 2 : a->ld, b_pitch = mxf4 ? b->ld / 2 : b->ld;
+        // packed e2m1 stays packed in shared memory for kind::mxf4 (16U4_ALIGN8B) and is expanded to one code per byte
+        // for the mixed kind (16U4_ALIGN16B); dims and boxes of both are in logical 4-bit elements, pitches in bytes
+        auto map_dtype = [&](uint32_t bits) {
+            return bits == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (mxf4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B);
+        };
+        const uint64_t a_pitch = a->bits == 4 ? a->ld / 2 : a->ld, b_pitch = b->bits == 4 ? b->ld / 2 : b->ld;
         uint64_t dims[3] = {pr.k, pr.m, a_groups};
         uint64_t strides[2] = {a_pitch, a_pitch * pr.m};
         const uint32_t slab = mxf4 ? 256u : 128u;    // one 128-byte slab of K per TMA box
         uint32_t box[3] = {slab, dg::kBlockM, 1};
-        rc = encode_map(&maps[0], dt, 3, a->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
+        rc = encode_map(&maps[0], map_dtype(a->bits), 3, a->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
         if (rc) return rc;
         uint64_t bdims[3] = {pr.k, pr.n, b_groups};
         uint64_t bstrides[2] = {b_pitch, b_pitch * pr.n};
         uint32_t bbox[3] = {slab, cfg.block_n / cfg.cluster_m, 1};
-        rc = encode_map(&maps[1], dt, 3, b->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
+        rc = encode_map(&maps[1], map_dtype(b->bits), 3, b->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
         if (rc) return rc;
     }
     const uint32_t sfa_cols = dg_sf_packed_cols(pr.k, a->gran_k), sfb_cols = dg_sf_packed_cols(pr.k, b->gran_k);
@@ -495,6 +499,12 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.num_accum_stages = cfg.num_accum_stages;
     p.gran_a = a->gran_k;
     p.gran_b = b->gran_k;
+    // measured on B200: a 16U4_ALIGN16B load (e2m1 expanded to one code per byte) fills 128 bytes of shared memory per
+    // 128 elements but signals only the 64 packed bytes it read on its barrier
+    p.tx_shift_a = (!mxf4 && a->bits == 4) ? 1 : 0;
+    p.tx_shift_b = (!mxf4 && b->bits == 4) ? 1 : 0;
+    p.fmt_a = a->bits == 8 ? 0u : 5u;
+    p.fmt_b = b->bits == 8 ? 0u : 5u;
     p.sf_a_cols = sfa_cols;
     p.sf_b_cols = sfb_cols;
     p.mk_alignment = align;

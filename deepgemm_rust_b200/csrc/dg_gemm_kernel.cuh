@@ -48,6 +48,8 @@ struct GemmParams {
     uint32_t num_stages;
     uint32_t num_accum_stages;
     uint32_t gran_a, gran_b;   // K elements per scale factor (32 or 128)
+    uint32_t tx_shift_a, tx_shift_b;   // 1 if the TMA load of that operand signals half the bytes its tile occupies (expanded e2m1)
+    uint32_t fmt_a, fmt_b;     // kind::mxf8f6f4 operand formats: 0 = e4m3, 5 = e2m1 held one code per byte in shared memory
     uint32_t sf_a_cols, sf_b_cols;  // packed words per row (per group) along K
     uint32_t num_splits;       // dense only: K is cut into this many ranges, each writing its own f32 partial (D's 3rd coordinate)
     uint32_t kb_per_split;     // k-blocks per range (a multiple of every scale-word period)
@@ -291,9 +293,10 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                             tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0),
                                         static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words));
                     }
-                    if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, a_bytes + b_bytes);
+                    const uint32_t tx_bytes = (a_bytes >> p.tx_shift_a) + (b_bytes >> p.tx_shift_b);
+                    if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, tx_bytes);
                     // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
-                    else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * (a_bytes + b_bytes));
+                    else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * tx_bytes);
                     for (uint32_t h = 0; h < halves; ++h) {
                         const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
                         uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
@@ -318,7 +321,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             Scheduler sched(p, kCtas);
             Tile t;
             uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0;
-            const uint32_t idesc = make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : 0u, kMXF4 ? 1u : 0u);
+            const uint32_t idesc = make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b);
             const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
 #ifdef DG_PROFILE

@@ -87,8 +87,11 @@ def test_heuristics_grouped_and_output_kinds():
     assert dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 4096, 7168, 16384)).num_splits == 1
     assert dg.best_config(dg.Sm100Desc(dg.GemmType.MGroupedMasked, 128, 4096, 16384, num_groups=2, expected_m=64)).num_splits == 1
     assert dg.best_config(dg.Sm100Desc(dg.GemmType.Batched, 128, 1024, 16384, num_groups=2, cd_dtype=2)).num_splits == 1
+    # e4m3 x e2m1 runs on the byte-operand kind: 128 K elements per 128-byte slab like e4m3 x e4m3
+    c = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 4096, 7168, 7168, a_bits=8, b_bits=4, gran_a=128, gran_b=32))
+    assert c.block_k in (128, 256)
     with pytest.raises(dg.DgError):
-        dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 128, 128, a_bits=8, b_bits=4))
+        dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 128, 128, a_bits=6, b_bits=4))
 
 
 def test_no_device_fails_loudly():

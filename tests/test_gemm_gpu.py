@@ -342,6 +342,27 @@ def test_dense_mxfp4(ctx, m, n, k, rule):
     assert O.calc_diff(to_f32(d), want) <= TIGHT_F32
 
 
+@pytest.mark.parametrize("a_bits,b_bits,gran8", [(8, 4, 128), (8, 4, 32), (4, 8, 128)])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 448, 1408)])
+def test_dense_mixed_fp8_fp4(ctx, m, n, k, a_bits, b_bits, gran8):
+    # e4m3 (per-128 or per-32 scales) against packed e2m1 (per-32 scales) on the byte-operand tensor-core kind
+    def operand(rows, bits, seed):
+        if bits == 8:
+            _, q, sf = fp8_operand_1d(rows, k, seed, gran8)
+            return q, sf, gran8
+        _, q, sf = fp4_operand(rows, k, seed, 1, 1)
+        return q, sf, 32
+    aq, asf, ga = operand(m, a_bits, 71)
+    bq, bsf, gb = operand(n, b_bits, 72)
+    d = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, dg.LpOperand(dev(aq), dev(asf), m, k, k, a_bits, ga), dg.LpOperand(dev(bq), dev(bsf), n, k, k, b_bits, gb),
+                        dg.Sm100Out.F32(d, n))
+    ctx.sync()
+    rows, cols = np.arange(m, dtype=np.uint32), np.arange(n, dtype=np.uint32)
+    want = O.lp_gemm_rows(aq, asf, a_bits, ga, 1, m, rows, bq, bsf, b_bits, gb, 1, n, cols, k)
+    assert O.calc_diff(to_f32(d), want) <= TIGHT_F32
+
+
 def test_m_grouped_mxfp4(ctx):
     groups, gm, n, k = 4, 128, 256, 512     # tests/e2e.rs:439-500
     _, aq, asf = fp4_operand(groups * gm, k, 61, 1, 1)
