@@ -92,6 +92,11 @@ _gemm_contig_static = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_static", C.c_
 _gemm_masked = _proto("dg_m_grouped_fp8_fp4_gemm_masked", C.c_int, _vp, C.POINTER(_LpOperand), _vp, C.POINTER(_LpOperand),
                       C.POINTER(_Out), _u32, _u32, C.POINTER(_Epilogue))
 _bmm = _proto("dg_fp8_fp4_bmm", C.c_int, _vp, C.POINTER(_LpOperand), C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_f32 = (_vp, _vp, _u32, _vp, _vp, _u32, _vp, _u32, _u32, _u32, _vp, _u32)
+_gemm_nt = _proto("dg_fp8_gemm_nt", C.c_int, *_f32)
+_gemm_nt_contig = _proto("dg_m_grouped_fp8_gemm_nt_contiguous", C.c_int, *_f32, _vp, _u32)
+_gemm_nt_masked = _proto("dg_m_grouped_fp8_gemm_nt_masked", C.c_int, *_f32, _vp, _u32, _u32)
+_bmm_nt = _proto("dg_fp8_bmm_nt", C.c_int, *_f32, _u32)
 _sf_packed_cols = _proto("dg_sf_packed_cols", _u32, _u32, _u32)
 _sf_aligned_rows = _proto("dg_sf_aligned_rows", _u32, _u32)
 _sf_words = _proto("dg_sf_words", _sz, _u32, _u32, _u32, _u32)
@@ -279,6 +284,42 @@ def fp8_fp4_bmm_dev(ctx, a, b, out, num_groups: int, epi=None):
     """ops_sm100.rs:864; a.rows = m and b.rows = n per group."""
     ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
     _check(_bmm(ctx._h, C.byref(ca), C.byref(cb), C.byref(co), num_groups, C.byref(ce)))
+
+
+@dataclass
+class Fp8Tensor:
+    """deepgemm/src/types.rs (Fp8Tensor): e4m3 bytes (rows, ld), K-major."""
+    data: torch.Tensor
+    rows: int
+    k: int
+    ld: int
+
+
+def _f32_args(ctx, a, a_sf_t, b, sfb, m, n, out, out_ld):
+    return (ctx._h, _vp(a.data.data_ptr()), a.ld, _vp(a_sf_t.data_ptr()), _vp(b.data.data_ptr()), b.ld, _vp(sfb.data_ptr()), m, n, a.k,
+            _vp(out.data_ptr()), out_ld)
+
+
+def fp8_gemm_nt_dev(ctx, a: Fp8Tensor, a_sf_t: torch.Tensor, b: Fp8Tensor, sfb: torch.Tensor, out: torch.Tensor, out_ld: int):
+    """deepgemm/src/ops.rs:328: f32 scales (a_sf_t from transform_sf_dev, sfb per 128x128 tile), bf16 out."""
+    _check(_gemm_nt(*_f32_args(ctx, a, a_sf_t, b, sfb, a.rows, b.rows, out, out_ld)))
+
+
+def m_grouped_fp8_gemm_nt_contiguous_dev(ctx, a, a_sf_t, b, sfb, out, out_ld, m_indices, num_groups: int):
+    """deepgemm/src/ops.rs:422; b.rows = num_groups * n."""
+    _check(_gemm_nt_contig(*_f32_args(ctx, a, a_sf_t, b, sfb, a.rows, b.rows // max(num_groups, 1), out, out_ld), _vp(m_indices.data_ptr()),
+                           num_groups))
+
+
+def m_grouped_fp8_gemm_nt_masked_dev(ctx, a, a_sf_t, b, sfb, out, out_ld, masked_m, num_groups: int, m_max: int, expected_m: int):
+    """deepgemm/src/ops.rs:535; a is (num_groups, m_max, k), b.rows = num_groups * n."""
+    _check(_gemm_nt_masked(*_f32_args(ctx, a, a_sf_t, b, sfb, m_max, b.rows // max(num_groups, 1), out, out_ld), _vp(masked_m.data_ptr()),
+                           num_groups, expected_m))
+
+
+def fp8_bmm_nt_dev(ctx, a, a_sf_t, b, sfb, out, out_ld, num_groups: int, m: int, n: int):
+    """deepgemm/src/ops.rs:635; a is (num_groups, m, k), b is (num_groups, n, k)."""
+    _check(_bmm_nt(*_f32_args(ctx, a, a_sf_t, b, sfb, m, n, out, out_ld), num_groups))
 
 
 def sf_packed_cols(k: int, gran_k: int) -> int:

@@ -71,6 +71,8 @@ struct dg_ctx {
     uint32_t group_ends_cap = 0;
     float* splitk_ws = nullptr;         // scratch for the f32 partial products of K-split GEMMs
     size_t splitk_ws_cap = 0;           // in floats
+    uint32_t* bridge_sf[2] = {nullptr, nullptr};   // packed scale words built from f32 scales by the f32-scale entry points
+    size_t bridge_sf_cap[2] = {0, 0};              // in words
 };
 
 extern "C" {
@@ -116,6 +118,8 @@ int dg_ctx_destroy(dg_ctx* ctx) {
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->group_ends) cudaFree(ctx->group_ends);
     if (ctx->splitk_ws) cudaFree(ctx->splitk_ws);
+    for (int i = 0; i < 2; ++i)
+        if (ctx->bridge_sf[i]) cudaFree(ctx->bridge_sf[i]);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return DG_OK;
@@ -613,6 +617,72 @@ int dg_fp8_fp4_bmm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, 
     if (num_groups == 0) return fail(DG_ERR_SHAPE, "num_groups must be positive");
     Problem pr = {DG_GEMM_BATCHED, a->rows, b->rows, a->k, num_groups, a->rows, nullptr};
     return launch_gemm(ctx, a, b, out, epi, pr);
+}
+
+// ------------------------------------------------------------ f32-scale entry points
+// The reference's older API hands scales over as f32 (activations transposed by transform_sf, weights one per
+// 128x128 tile).  Like the reference on Blackwell (ops_sm100.rs:1414-1605) these entry points pack the exponents into
+// UE8M0 words (mantissas are dropped: the scales must be powers of two to be exact) and run the block-scaled kernel.
+static int bridge_common(dg_ctx* ctx, uint32_t type, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
+                         const float* sfb, uint32_t m, uint32_t n, uint32_t k, uint32_t groups, const uint32_t* layout, uint32_t expected_m,
+                         uint16_t* out, uint32_t out_ld) {
+    if (!ctx || !a || !a_sf_t || !b || !sfb || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (k == 0 || k % 128 != 0) return fail(DG_ERR_SHAPE, "k (%u) must be a multiple of 128 (per-128-channel scaling)", k);
+    if (n % 8 != 0) return fail(DG_ERR_SHAPE, "n (%u) must be a multiple of 8", n);
+    if (groups == 0) return fail(DG_ERR_SHAPE, "num_groups must be positive");
+    const bool contiguous = type == DG_GEMM_M_GROUPED_CONTIGUOUS;
+    const uint32_t a_groups = (type == DG_GEMM_NORMAL || contiguous) ? 1 : groups;
+    const uint32_t b_groups = type == DG_GEMM_NORMAL ? 1 : groups;
+    const size_t need[2] = {dg_sf_words(m * a_groups, k, 128, a_groups), dg_sf_words(n * b_groups, k, 128, b_groups)};
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    for (int i = 0; i < 2; ++i) {
+        if (ctx->bridge_sf_cap[i] >= need[i]) continue;
+        if (ctx->bridge_sf[i]) { cudaFree(ctx->bridge_sf[i]); ctx->bridge_sf[i] = nullptr; ctx->bridge_sf_cap[i] = 0; }
+        DG_CUDA(cudaMalloc(&ctx->bridge_sf[i], need[i] * 4));
+        ctx->bridge_sf_cap[i] = need[i];
+    }
+    // padding rows of the packed layouts must read as a valid exponent
+    DG_CUDA(cudaMemsetAsync(ctx->bridge_sf[0], 0, need[0] * 4, ctx->stream));
+    DG_CUDA(cudaMemsetAsync(ctx->bridge_sf[1], 0, need[1] * 4, ctx->stream));
+    int rc = dg_transform_sf_t_packed_ue8m0(ctx, a_sf_t, m * a_groups, k, 128, a_groups, ctx->bridge_sf[0]);
+    if (rc) return rc;
+    rc = dg_transform_sf2d_packed_ue8m0(ctx, sfb, k / 128, n * b_groups, k, b_groups, ctx->bridge_sf[1]);
+    if (rc) return rc;
+    dg_lp_operand a_op = {a, ctx->bridge_sf[0], m, k, a_ld, 8, 128, 0, static_cast<size_t>(m) * a_groups * a_ld, need[0]};
+    dg_lp_operand b_op = {b, ctx->bridge_sf[1], type == DG_GEMM_BATCHED || type == DG_GEMM_NORMAL ? n : n * groups, k, b_ld, 8, 128, 0,
+                          static_cast<size_t>(n) * b_groups * b_ld, need[1]};
+    dg_out o = {DG_OUT_BF16, out, out_ld, nullptr, static_cast<size_t>(m) * a_groups * out_ld, 0};
+    switch (type) {
+        case DG_GEMM_NORMAL: return dg_fp8_fp4_gemm(ctx, &a_op, &b_op, &o, nullptr);
+        case DG_GEMM_M_GROUPED_CONTIGUOUS:
+            return dg_m_grouped_fp8_fp4_gemm_contiguous(ctx, &a_op, reinterpret_cast<const int32_t*>(layout), &b_op, &o, groups, nullptr);
+        case DG_GEMM_M_GROUPED_MASKED:
+            return dg_m_grouped_fp8_fp4_gemm_masked(ctx, &a_op, reinterpret_cast<const int32_t*>(layout), &b_op, &o, groups, expected_m, nullptr);
+        default: return dg_fp8_fp4_bmm(ctx, &a_op, &b_op, &o, groups, nullptr);
+    }
+}
+
+int dg_fp8_gemm_nt(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld, const float* sfb, uint32_t m,
+                   uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld) {
+    return bridge_common(ctx, DG_GEMM_NORMAL, a, a_ld, a_sf_t, b, b_ld, sfb, m, n, k, 1, nullptr, m, out, out_ld);
+}
+int dg_m_grouped_fp8_gemm_nt_contiguous(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
+                                        const float* sfb, uint32_t m_total, uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld,
+                                        const int32_t* m_indices, uint32_t num_groups) {
+    if (!m_indices) return fail(DG_ERR_SHAPE, "null argument");
+    return bridge_common(ctx, DG_GEMM_M_GROUPED_CONTIGUOUS, a, a_ld, a_sf_t, b, b_ld, sfb, m_total, n, k, num_groups,
+                         reinterpret_cast<const uint32_t*>(m_indices), m_total, out, out_ld);
+}
+int dg_m_grouped_fp8_gemm_nt_masked(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
+                                    const float* sfb, uint32_t m_max, uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld,
+                                    const int32_t* masked_m, uint32_t num_groups, uint32_t expected_m) {
+    if (!masked_m) return fail(DG_ERR_SHAPE, "null argument");
+    return bridge_common(ctx, DG_GEMM_M_GROUPED_MASKED, a, a_ld, a_sf_t, b, b_ld, sfb, m_max, n, k, num_groups,
+                         reinterpret_cast<const uint32_t*>(masked_m), expected_m, out, out_ld);
+}
+int dg_fp8_bmm_nt(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld, const float* sfb, uint32_t m,
+                  uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld, uint32_t num_groups) {
+    return bridge_common(ctx, DG_GEMM_BATCHED, a, a_ld, a_sf_t, b, b_ld, sfb, m, n, k, num_groups, nullptr, m, out, out_ld);
 }
 
 // ------------------------------------------------------- entry point that allocates nothing

@@ -124,6 +124,23 @@ int dg_m_grouped_fp8_fp4_gemm_masked(dg_ctx* ctx, const dg_lp_operand* a, const 
 int dg_fp8_fp4_bmm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, uint32_t num_groups,
                    const dg_epilogue* epi);
 
+/* The older f32-scale API (deepgemm/src/ops.rs:328 fp8_gemm_nt_dev, :422 / :535 the grouped variants, :635
+ * fp8_bmm_nt_dev), which on Blackwell the reference routes through ops_sm100.rs:1414-1605.  a: e4m3 (rows, a_ld);
+ * a_sf_t: the output of dg_transform_sf for a's (rows, k/128) f32 scales; b: e4m3 (num_groups * n, b_ld); sfb:
+ * (num_groups * n / 128, k/128) f32 tile scales; out: bf16.  Exactly like the reference's bridge, only the exponent of
+ * each f32 scale is used (scales must be powers of two to be exact).  Packed scale words are built in
+ * context-owned scratch. */
+int dg_fp8_gemm_nt(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld, const float* sfb, uint32_t m,
+                   uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld);
+int dg_m_grouped_fp8_gemm_nt_contiguous(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
+                                        const float* sfb, uint32_t m_total, uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld,
+                                        const int32_t* m_indices, uint32_t num_groups);
+int dg_m_grouped_fp8_gemm_nt_masked(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
+                                    const float* sfb, uint32_t m_max, uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld,
+                                    const int32_t* masked_m, uint32_t num_groups, uint32_t expected_m);
+int dg_fp8_bmm_nt(dg_ctx* ctx, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld, const float* sfb, uint32_t m,
+                  uint32_t n, uint32_t k, uint16_t* out, uint32_t out_ld, uint32_t num_groups);
+
 /* ops_sm100.rs:1091-1098 (sf_packed_cols, sf_aligned_rows) and the size of alloc_sf (:1107). */
 uint32_t dg_sf_packed_cols(uint32_t k, uint32_t gran_k);
 uint32_t dg_sf_aligned_rows(uint32_t rows);
