@@ -101,6 +101,7 @@ _sf_packed_cols = _proto("dg_sf_packed_cols", _u32, _u32, _u32)
 _sf_aligned_rows = _proto("dg_sf_aligned_rows", _u32, _u32)
 _sf_words = _proto("dg_sf_words", _sz, _u32, _u32, _u32, _u32)
 _cast_fp8 = _proto("dg_cast_bf16_to_fp8_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp)
+_silu_cast = _proto("dg_silu_mul_cast_fp8_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp)
 _cast_fp4 = _proto("dg_cast_bf16_to_fp4_packed_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, C.c_int, _vp, _vp)
 _transform_sf = _proto("dg_transform_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _vp)
 _tsf1d = _proto("dg_transform_sf1d_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp)
@@ -343,6 +344,16 @@ def cast_bf16_to_fp8_sf_dev(ctx, src: torch.Tensor, src_ld: int, rows: int, k: i
     dst = torch.empty((rows, k), dtype=torch.uint8, device=src.device)
     sf = alloc_sf(ctx, rows, k, gran_k, num_groups)
     _check(_cast_fp8(ctx._h, _vp(src.data_ptr()), src_ld, rows, k, gran_k, num_groups, _vp(dst.data_ptr()), _vp(sf.data_ptr())))
+    return dst, sf
+
+
+def silu_mul_cast_fp8_sf_dev(ctx, gate_up: torch.Tensor, src_ld: int, rows: int, n: int, gran_k: int = 128, num_groups: int = 1
+                             ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """moe.rs:273-296 (silu(gate) * up on a (rows, 2n) bf16 matrix) fused with the FP8 quantiser of the
+    activation: returns (e4m3 bytes (rows, n), packed UE8M0 words) ready to be the next grouped GEMM's A."""
+    dst = torch.empty((rows, n), dtype=torch.uint8, device=gate_up.device)
+    sf = alloc_sf(ctx, rows, n, gran_k, num_groups)
+    _check(_silu_cast(ctx._h, _vp(gate_up.data_ptr()), src_ld, rows, n, gran_k, num_groups, _vp(dst.data_ptr()), _vp(sf.data_ptr())))
     return dst, sf
 
 

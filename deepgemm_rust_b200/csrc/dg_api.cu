@@ -177,7 +177,11 @@ uint32_t dg_get_theoretical_mk_alignment_for_contiguous_layout(uint32_t arch_maj
 // Tile choice for 148 SMs / 227 KB shared memory / 512 TMEM columns.  A rows always ride the
 // UMMA M dimension (128 per tile); BLOCK_N is picked from the widths the epilogue of the output
 // type can store, minimising waves x per-tile cost; stages fill the shared memory left over.
-int dg_best_config(const dg_desc* d, dg_config* out) {
+static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out);
+int dg_best_config(const dg_desc* d, dg_config* out) { return choose_config(d, 0, out); }
+
+// no_k_ranges: the caller adds into the output (K ranges would need the sum to be written, not added)
+static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out) {
     if (d == nullptr || out == nullptr) return fail(DG_ERR_SHAPE, "null argument");
     if ((d->a_bits != 8 && d->a_bits != 4) || (d->b_bits != 8 && d->b_bits != 4)) return fail(DG_ERR_SHAPE, "operand bits must be 8 or 4");
     // two packed e2m1 operands run on kind::mxf4 (256 elements per 128-byte slab); an e4m3 x e2m1 pair runs on
@@ -242,7 +246,7 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
             const double per_kb = halves * (mma > feed ? mma : feed) + 150.0;
             // K ranges (dense GEMMs with f32-summable outputs only): each range is a multiple of 4 k-blocks so scale words
             // never straddle ranges; the partial sums cost a second small kernel (launch + S reads of the M x N f32 tile set)
-            const bool may_split = d->gemm_type == DG_GEMM_NORMAL && d->cd_dtype != DG_OUT_FP8 && d->n % 4 == 0;
+            const bool may_split = d->gemm_type == DG_GEMM_NORMAL && d->cd_dtype != DG_OUT_FP8 && d->n % 4 == 0 && !no_k_ranges;
             for (uint32_t splits = 1; splits <= 16; ++splits) {
                 if (splits > 1 && (!may_split || halves > 1)) break;
                 if (force_splits && static_cast<uint32_t>(atoi(force_splits)) != splits) continue;
@@ -382,7 +386,6 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     if (out->kind == DG_OUT_FP8 && (e.has_alpha || e.accumulate))
         return fail(DG_ERR_SHAPE, "the FP8-quantized output cannot combine alpha/accumulation");
     if (e.accumulate && e.has_alpha) return fail(DG_ERR_SHAPE, "alpha and accumulation are mutually exclusive");
-    if (e.accumulate) return fail(DG_ERR_UNSUPPORTED, "accumulation into the output is not built yet");
     if (a->k != b->k) return fail(DG_ERR_SHAPE, "a.k (%u) != b.k (%u)", a->k, b->k);
     if (pr.m == 0 || pr.n == 0) return DG_OK;
     const bool contiguous = pr.type == DG_GEMM_M_GROUPED_CONTIGUOUS;
@@ -409,7 +412,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     dg_desc desc = {pr.type, pr.m, pr.n, pr.k, pr.groups, pr.expected_m, a->bits, b->bits, a->gran_k, b->gran_k,
                     static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms)};
     dg_config cfg;
-    rc = dg_best_config(&desc, &cfg);
+    rc = choose_config(&desc, e.accumulate ? 1u : 0u, &cfg);
     if (rc) return rc;
     static const bool print_cfg = [] { const char* v = getenv("DG_PRINT_CONFIGS"); return v && strcmp(v, "0") != 0; }();
     if (print_cfg)
@@ -512,6 +515,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.sf_a_cols = sfa_cols;
     p.sf_b_cols = sfb_cols;
     p.mk_alignment = align;
+    p.accumulate = e.accumulate ? 1 : 0;
     p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges alpha is applied to the sum
     p.alpha = e.alpha;
     p.sfd = out->sfd;
@@ -751,11 +755,12 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous_static(int device, void* cuda_stream, c
 
 // ------------------------------------------------------------------ quantise / re-layout
 static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran, uint32_t groups, int rule,
-                       bool fp4, uint8_t* dst, uint32_t* sf) {
+                       bool fp4, uint8_t* dst, uint32_t* sf, bool silu_mul = false) {
     if (!ctx || !src || !dst || !sf) return fail(DG_ERR_SHAPE, "null argument");
     if (groups == 0) groups = 1;
     if (rows % groups != 0) return fail(DG_ERR_SHAPE, "rows (%u) must be a multiple of num_groups (%u)", rows, groups);
-    if (src_ld < k || src_ld % 8 != 0) return fail(DG_ERR_SHAPE, "src_ld (%u) must be >= k and a multiple of 8 elements", src_ld);
+    if (src_ld < (silu_mul ? 2 * k : k) || src_ld % 8 != 0)
+        return fail(DG_ERR_SHAPE, "src_ld (%u) must cover the %u source columns and be a multiple of 8 elements", src_ld, silu_mul ? 2 * k : k);
     if (reinterpret_cast<uintptr_t>(src) % 16 != 0 || reinterpret_cast<uintptr_t>(dst) % 16 != 0)
         return fail(DG_ERR_SHAPE, "src and dst must be 16-byte aligned");
     if (rows == 0) return DG_OK;
@@ -770,7 +775,9 @@ static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32
     if (units > 0x7FFFFFFFull) return fail(DG_ERR_SHAPE, "matrix too large for one launch");
     const uint32_t blocks = static_cast<uint32_t>(units);
     DG_CUDA(cudaSetDevice(ctx->ordinal));
-    if (fp4) dg::dg_cast_kernel<32, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    if (silu_mul && gran == 32) dg::dg_cast_kernel<32, false, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    else if (silu_mul) dg::dg_cast_kernel<128, false, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    else if (fp4) dg::dg_cast_kernel<32, true><<<blocks, 256, 0, ctx->stream>>>(p);
     else if (gran == 32) dg::dg_cast_kernel<32, false><<<blocks, 256, 0, ctx->stream>>>(p);
     else dg::dg_cast_kernel<128, false><<<blocks, 256, 0, ctx->stream>>>(p);
     DG_CUDA(cudaGetLastError());
@@ -782,6 +789,13 @@ int dg_cast_bf16_to_fp8_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, ui
     if (gran_k != 32 && gran_k != 128) return fail(DG_ERR_SHAPE, "gran_k must be 32 or 128");
     if (k == 0 || k % (gran_k * 4) != 0) return fail(DG_ERR_SHAPE, "k must be a multiple of %u for gran %u", gran_k * 4, gran_k);
     return cast_common(ctx, src, src_ld, rows, k, gran_k, num_groups, 0, false, dst, sf);
+}
+
+int dg_silu_mul_cast_fp8_sf(dg_ctx* ctx, const uint16_t* gate_up, uint32_t src_ld, uint32_t rows, uint32_t n, uint32_t gran_k,
+                            uint32_t num_groups, uint8_t* dst, uint32_t* sf) {
+    if (gran_k != 32 && gran_k != 128) return fail(DG_ERR_SHAPE, "gran_k must be 32 or 128");
+    if (n == 0 || n % (gran_k * 4) != 0) return fail(DG_ERR_SHAPE, "n must be a multiple of %u for gran %u", gran_k * 4, gran_k);
+    return cast_common(ctx, gate_up, src_ld, rows, n, gran_k, num_groups, 0, false, dst, sf, true);
 }
 
 int dg_cast_bf16_to_fp4_packed_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,

@@ -30,8 +30,29 @@ DG_DEVICE uint32_t sf_exp_e2m1(float amax, int rule) {
     return e < 1u ? 1u : e;
 }
 
+// bf16(silu(g) * u) as f32, silu(g) = g / (1 + exp(-g)).  exp is spelled out in correctly rounded f32
+// operations (range reduction by ln 2 in two parts, degree-7 Taylor polynomial on |r| <= ln2/2, exact scaling
+// by 2^n), so a host restatement with fmaf/rintf gives the same bits; it is within 2 ulp of exp.
+DG_DEVICE float silu_mul_bf16(float g, float u) {
+    const float x = fminf(fmaxf(-g, -87.0f), 88.0f);
+    const float n = rintf(__fmul_rn(x, 1.44269504f));
+    float r = __fmaf_rn(n, -0.693145752f, x);
+    r = __fmaf_rn(n, -1.42860677e-6f, r);
+    float q = 1.0f / 5040.0f;
+    q = __fmaf_rn(q, r, 1.0f / 720.0f);
+    q = __fmaf_rn(q, r, 1.0f / 120.0f);
+    q = __fmaf_rn(q, r, 1.0f / 24.0f);
+    q = __fmaf_rn(q, r, 1.0f / 6.0f);
+    q = __fmaf_rn(q, r, 0.5f);
+    q = __fmaf_rn(q, __fmul_rn(r, r), r);
+    const float e = __fmul_rn(__fadd_rn(q, 1.0f), __uint_as_float(static_cast<uint32_t>(static_cast<int32_t>(n) + 127) << 23));
+    const float silu = -g > 88.0f ? 0.0f : __fdiv_rn(g, __fadd_rn(1.0f, e));   // |g exp(g)| < 5e-37 there
+    const float act = __fmul_rn(silu, u);
+    return __uint_as_float(pack_bf16x2(0.0f, act) & 0xFFFF0000u);
+}
+
 struct CastParams {
-    const uint16_t* src;   // (rows, src_ld) bf16
+    const uint16_t* src;   // (rows, src_ld) bf16; with kSiluMul: gate at [0, k), up at [k, 2k) of each row
     uint8_t* dst;          // (rows, k) e4m3 or (rows, k/2) packed e2m1
     uint32_t* sf;          // packed scale words
     uint32_t src_ld, rows, k, group_rows, sf_cols, sf_stride;
@@ -41,7 +62,9 @@ struct CastParams {
 // One warp quantises 1024 consecutive K elements of one row: four 16-byte loads per lane, all issued
 // before the first use (elements [256*h + 8*lane, +8) for h = 0..3).  kGran = 128: 16 lanes share a scale,
 // the warp produces two scale words.  kGran = 32: 4 lanes share a scale, the warp produces 8 words.
-template <uint32_t kGran, bool kFp4>
+// kSiluMul: the value quantised is bf16(silu(gate) * up) (moe.rs:273-296, layout.rs:218-233 followed by the
+// activation quantiser), read from a (rows, 2k) gate|up matrix; the bf16 activation never reaches memory.
+template <uint32_t kGran, bool kFp4, bool kSiluMul = false>
 __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
     constexpr uint32_t kLoads = 4, kSeg = 256 * kLoads;
     // a block takes 8 consecutive rows (one per warp) of one segment, so that the scale words of a word column,
@@ -55,18 +78,26 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
     const bool live = row < p.rows;
     const uint16_t* src_row = p.src + static_cast<size_t>(live ? row : 0) * p.src_ld;
 
-    uint4 raw[kLoads];
+    uint4 raw[kLoads], raw_up[kSiluMul ? kLoads : 1];
     uint32_t k0[kLoads];
     #pragma unroll
     for (uint32_t h = 0; h < kLoads; ++h) {
         k0[h] = seg * kSeg + h * 256 + lane * 8;
         raw[h] = (live && k0[h] < p.k) ? __ldg(reinterpret_cast<const uint4*>(src_row + k0[h])) : make_uint4(0, 0, 0, 0);
+        if constexpr (kSiluMul)
+            raw_up[h] = (live && k0[h] < p.k) ? __ldg(reinterpret_cast<const uint4*>(src_row + p.k + k0[h])) : make_uint4(0, 0, 0, 0);
     }
     uint32_t exps[kLoads];
     #pragma unroll
     for (uint32_t h = 0; h < kLoads; ++h) {
         float v[8] = {bf16_lo(raw[h].x), bf16_hi(raw[h].x), bf16_lo(raw[h].y), bf16_hi(raw[h].y),
                       bf16_lo(raw[h].z), bf16_hi(raw[h].z), bf16_lo(raw[h].w), bf16_hi(raw[h].w)};
+        if constexpr (kSiluMul) {
+            const float u[8] = {bf16_lo(raw_up[h].x), bf16_hi(raw_up[h].x), bf16_lo(raw_up[h].y), bf16_hi(raw_up[h].y),
+                                bf16_lo(raw_up[h].z), bf16_hi(raw_up[h].z), bf16_lo(raw_up[h].w), bf16_hi(raw_up[h].w)};
+            #pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) v[i] = silu_mul_bf16(v[i], u[i]);
+        }
         float amax = 0.0f;
         #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));

@@ -55,6 +55,7 @@ struct GemmParams {
     uint32_t kb_per_split;     // k-blocks per range (a multiple of every scale-word period)
     uint32_t mk_alignment;     // contiguous layout: every group starts at a multiple of this
     uint32_t has_alpha;
+    uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
     float alpha;
     uint32_t sfd_stride;       // output scale words: stride between word columns (fp8 output)
     const uint32_t* grouped_layout;  // contiguous: end row of each group; masked: valid rows per group
@@ -560,8 +561,10 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (col0 < p.n && row0 < t.m_end)
-                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.gd));
+                        if (col0 < p.n && row0 < t.m_end) {
+                            if (p.accumulate) tma_reduce_add_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.gd));
+                            else tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.gd));
+                        }
                         tma_store_commit();
                     }
                     buf_idx ^= 1;

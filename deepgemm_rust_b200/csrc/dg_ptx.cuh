@@ -152,6 +152,13 @@ DG_DEVICE void tma_store_3d(const void* tmap, const void* smem, int32_t x, int32
                  "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z)
                  : "memory");
 }
+// Same tile, added to what global memory holds (element type of the tensor map: f32 or bf16).
+DG_DEVICE void tma_reduce_add_3d(const void* tmap, const void* smem, int32_t x, int32_t y, int32_t z) {
+    asm volatile("cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(tmap)),
+                 "r"(smem_u32(smem)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
 DG_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 DG_DEVICE void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }

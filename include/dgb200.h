@@ -75,7 +75,7 @@ typedef struct {
 typedef struct {
     float alpha;
     int has_alpha;
-    int accumulate;       /* not supported: DG_ERR_UNSUPPORTED */
+    int accumulate;       /* D += A.B^T (dense, masked and batched calls; bf16 or f32 outputs; not with alpha) */
     uint32_t tc_util;     /* accepted, ignored (100 = unthrottled) */
 } dg_epilogue;
 
@@ -156,6 +156,13 @@ enum { DG_SF_RULE_REFERENCE_CPU = 0, DG_SF_RULE_RANGE_FIT = 1 };
  * except for the alignment padding rows, which are left untouched). */
 int dg_cast_bf16_to_fp8_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran_k,
                            uint32_t num_groups, uint8_t* dst, uint32_t* sf);
+/* moe.rs:273-296 with layout.rs:218-233 (deepgemm_silu_mul_bf16), fused with the activation quantiser the
+ * second grouped GEMM needs: gate_up is (rows, 2n) bf16 with gate = [:, :n] and up = [:, n:]; the value
+ * quantised is bf16(silu(gate) * up), silu(g) = g / (1 + exp(-g)); output as dg_cast_bf16_to_fp8_sf gives
+ * for that bf16 matrix ((rows, n) e4m3 and packed UE8M0 words), without writing it. */
+int dg_silu_mul_cast_fp8_sf(dg_ctx* ctx, const uint16_t* gate_up, uint32_t src_ld, uint32_t rows, uint32_t n, uint32_t gran_k,
+                            uint32_t num_groups, uint8_t* dst, uint32_t* sf);
+
 /* ops_sm100.rs:1135 (cast_bf16_to_fp4_packed_sf_dev): dst rows*k/2 bytes. */
 int dg_cast_bf16_to_fp4_packed_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
                                   int sf_rule, uint8_t* dst, uint32_t* sf);

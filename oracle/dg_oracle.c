@@ -577,6 +577,36 @@ DGO_API void dgo_moe_combine(const uint16_t* rows, size_t pitch, const int32_t* 
         }
 }
 
+/* SiLU-and-mul (cuda/layout.rs:218-233 as called from moe.rs:273-296): out[r,c] = bf16(silu(gate) * up) on a
+ * (rows, 2n) gate|up matrix of bf16 bits, silu(g) = g / (1 + exp(-g)).  The reference's device code uses the
+ * fast-math exponential, which no host function reproduces bit for bit; exp is therefore written out here
+ * (and identically in the CUDA kernel) in correctly rounded f32 steps: n = rint(x * log2 e), r = x - n ln2 in
+ * two parts, a degree-7 Taylor polynomial on |r| <= ln2/2, times 2^n; gate values below -88 give 0.  Parity unpinned: a test bounds the
+ * distance to the f64 formula instead. */
+static float dgo_silu_mul_one(float g, float u) {
+    float x = fminf(fmaxf(-g, -87.0f), 88.0f);
+    float n = rintf(x * 1.44269504f);
+    float r = fmaf(n, -0.693145752f, x);
+    r = fmaf(n, -1.42860677e-6f, r);
+    float q = 1.0f / 5040.0f;
+    q = fmaf(q, r, 1.0f / 720.0f);
+    q = fmaf(q, r, 1.0f / 120.0f);
+    q = fmaf(q, r, 1.0f / 24.0f);
+    q = fmaf(q, r, 1.0f / 6.0f);
+    q = fmaf(q, r, 0.5f);
+    q = fmaf(q, r * r, r);
+    float e = (q + 1.0f) * u2f((uint32_t)((int32_t)n + 127) << 23);
+    float silu = -g > 88.0f ? 0.0f : g / (1.0f + e);   /* |g exp(g)| < 5e-37 there */
+    float act = silu * u;
+    return dgo_bf16_to_f32(dgo_f32_to_bf16(act));
+}
+DGO_API void dgo_silu_mul_bf16(const uint16_t* gate_up, uint32_t ld, uint32_t rows, uint32_t n, uint16_t* out) {
+    for (uint32_t r = 0; r < rows; ++r)
+        for (uint32_t c = 0; c < n; ++c)
+            out[(size_t)r * n + c] = dgo_f32_to_bf16(dgo_silu_mul_one(dgo_bf16_to_f32(gate_up[(size_t)r * ld + c]),
+                                                                      dgo_bf16_to_f32(gate_up[(size_t)r * ld + n + c])));
+}
+
 /* 1 - 2*sum(xy)/sum(x^2+y^2) in f64 (the tolerance metric; the reference has
  * no such function, the benchmark contract defines it). */
 DGO_API double dgo_calc_diff(const float* x, const float* y, size_t n) {

@@ -325,6 +325,18 @@ def moe_combine(rows_bits, pos, w):
     return out
 
 
+_silu_mul = _sig("dgo_silu_mul_bf16", None, _u16p, C.c_uint32, C.c_uint32, C.c_uint32, _u16p)
+
+
+def silu_mul_bf16(gate_up_bits):
+    """(rows, 2n) bf16 bits [gate | up] -> (rows, n) bf16 bits of silu(gate) * up (cuda/layout.rs:218-233)."""
+    gate_up_bits = np.ascontiguousarray(gate_up_bits, np.uint16)
+    rows, ld = gate_up_bits.shape
+    out = np.zeros((rows, ld // 2), np.uint16)
+    _silu_mul(gate_up_bits, ld, rows, ld // 2, out)
+    return out
+
+
 def calc_diff(x, y):
     x = np.ascontiguousarray(x, np.float32).reshape(-1)
     y = np.ascontiguousarray(y, np.float32).reshape(-1)

@@ -137,6 +137,35 @@ def test_dense_f32_and_alpha(ctx):
     run_dense(ctx, 128, 96, 512, out_kind=1, alpha=3.0)
 
 
+@pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("out_kind", [0, 1])
+def test_dense_accumulate_adds_into_the_output(ctx, out_kind, ctas, monkeypatch):
+    # D += A.B^T (with_accumulation, ops_sm100.rs:150): tiles are added to what the output holds. f32 outputs add
+    # in f32; bf16 outputs add the bf16-rounded tile to the bf16 addend and round once more, so the bound is
+    # two bf16 roundings. Ragged M and N: rows and columns outside the problem must stay untouched.
+    monkeypatch.setenv("DG_CTAS", str(ctas))
+    m, n, k, ld = 300, 456, 1152, 512
+    _, aq, asf = fp8_operand_1d(m, k, 77)
+    _, bq, bsf = fp8_operand_1d(n, k, 78)
+    want = O.lp_gemm_rows(aq, asf, 8, 128, 1, m, np.arange(m), bq, bsf, 8, 128, 1, n, np.arange(n), k)
+    dtype = torch.bfloat16 if out_kind == 0 else torch.float32
+    base = (torch.randn((m + 4, ld), device="cuda") * float(np.abs(want).mean())).to(dtype)
+    d = base.clone()
+    a, b = lp(aq, asf, m, k), lp(bq, bsf, n, k)
+    out = dg.Sm100Out(out_kind, d, ld)
+    dg.fp8_fp4_gemm_dev(ctx, a, b, out, dg.Sm100Epilogue(accumulate=True))
+    ctx.sync()
+    got, base_n = to_f32(d), to_f32(base)
+    assert np.array_equal(got[m:], base_n[m:]) and np.array_equal(got[:, n:], base_n[:, n:])
+    diff = O.calc_diff(got[:m, :n], want + base_n[:m, :n])
+    assert diff <= (2 * TIGHT_BF16 if out_kind == 0 else TIGHT_F32), diff
+    # a second call adds the product once more
+    dg.fp8_fp4_gemm_dev(ctx, a, b, out, dg.Sm100Epilogue(accumulate=True))
+    ctx.sync()
+    diff = O.calc_diff(to_f32(d)[:m, :n], 2 * want + base_n[:m, :n])
+    assert diff <= (3 * TIGHT_BF16 if out_kind == 0 else TIGHT_F32), diff
+
+
 @pytest.mark.parametrize("m", [128, 4096])
 @pytest.mark.parametrize("n,k", [(2112, 7168), (24576, 1536), (7168, 16384), (4096, 7168), (7168, 2048)])
 def test_dense_fp8_full_size_sampled(ctx, m, n, k):
@@ -396,7 +425,6 @@ def test_argument_errors(ctx):
     sfd = torch.zeros(128, dtype=torch.int32, device="cuda")
     assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.Fp8(d8, 128, sfd))) == "Shape"      # ops_sm100.rs:727
     assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, out, dg.Sm100Epilogue(alpha=2.0, accumulate=True))) == "Shape"  # :150
-    assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, out, dg.Sm100Epilogue(accumulate=True))) == "Unsupported"
     bad = dg.LpOperand(a.data, a.sf, 128, 512, 512, 8, 64)
     assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, bad, b, out)) == "Shape"                               # :52
     bad = dg.LpOperand(a.data, a.sf, 256, 512, 512)

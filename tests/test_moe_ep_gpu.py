@@ -56,7 +56,7 @@ def test_row_movers_bit_exact(ctx):
 
 
 def test_expert_parallel_step_single_rank(ctx):
-    experts, topk, tokens, hidden, n1, k2, n2 = 8, 2, 200, 512, 256, 256, 384
+    experts, topk, tokens, hidden, n1, k2, n2 = 8, 2, 200, 512, 1024, 512, 384
     g = torch.Generator().manual_seed(9)
     logits = torch.randn((tokens, experts), generator=g)
     probs = torch.softmax(logits, -1)
@@ -96,11 +96,26 @@ def test_expert_parallel_step_single_rank(ctx):
         want = O.lp_gemm_rows(arena, a_sf_np, 8, 128, 1, plan.m_pad, rows, w1q, w1sf, 8, 128, experts, n1,
                               np.arange(e * n1, (e + 1) * n1, dtype=np.uint32), hidden)
         assert O.calc_diff(hn[rows.astype(np.int64)], want) <= 2e-5
-    # grouped GEMM 2 takes an independent operand of the arena's row count (the benchmark's two GEMMs are independent)
-    _, actq, actsf = fp8_operand_1d(plan.m_pad, k2, 84)
+    # silu(gate) * up of GEMM 1's output, quantised for GEMM 2: bit-exact with the two oracle steps on the same bf16 bits
+    actq, actsf = dg.silu_mul_cast_fp8_sf_dev(ctx, h, n1, plan.m_pad, k2, 128)
+    ctx.sync()
+    h_bits = h.view(torch.int16).cpu().numpy().view(np.uint16)
+    want_q, want_sf = O.cast_bf16_to_fp8_sf(O.silu_mul_bf16(h_bits), k2, 128)
+    actq_np, actsf_np = actq.cpu().numpy(), actsf.cpu().numpy().view(np.uint32)
+    assert np.array_equal(actq_np, want_q) and np.array_equal(actsf_np, want_sf)
+    # grouped GEMM 2 consumes the activation
     y = torch.zeros((plan.m_pad, n2), dtype=torch.bfloat16, device="cuda")
-    dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(dev(actq), dev(actsf), plan.m_pad, k2, k2), plan.m_indices,
+    dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(actq, actsf, plan.m_pad, k2, k2), plan.m_indices,
                                              dg.LpOperand(dev(w2q), dev(w2sf), experts * n2, k2, k2), dg.Sm100Out.Bf16(y, n2), experts)
+    ctx.sync()
+    yn = to_f32(y)
+    for e in range(experts):
+        rows = valid[m_idx[valid] == e].astype(np.uint32)
+        if rows.size == 0:
+            continue
+        want = O.lp_gemm_rows(actq_np, actsf_np, 8, 128, 1, plan.m_pad, rows, w2q, w2sf, 8, 128, experts, n2,
+                              np.arange(e * n2, (e + 1) * n2, dtype=np.uint32), k2)
+        assert O.calc_diff(yn[rows.astype(np.int64)], want) <= 2e-5
     out = ep.combine(plan, y, topw.cuda().contiguous())
     ctx.sync()
     # combine: token t gets sum_j w[t,j] * y[arena row of pair (t,j)], bit-exact with the oracle reduction

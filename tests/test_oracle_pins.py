@@ -277,6 +277,25 @@ def test_sf_transforms():
     assert np.array_equal(w2d, O.transform_sf1d_packed(np.repeat(sf2, 128, axis=0), k, 128))
 
 
+def test_silu_mul_restatement_tracks_the_formula():
+    # cuda/layout.rs:231 computes g / (1 + exp(-g)) * u in f32 with the device's fast exponential and rounds to bf16;
+    # the restatement's explicit exponential must land on the bf16 nearest the f64 value, or its neighbour
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((64, 1024)) * 6).astype(np.float32)
+    bits = O.bf16_bits(x)
+    got_bits = O.silu_mul_bf16(bits)
+    xb = O.bf16_to_f32_array(bits).astype(np.float64)
+    g, u = xb[:, :512], xb[:, 512:]
+    want = g / (1.0 + np.exp(-g)) * u
+    want_bits = O.bf16_bits(want.astype(np.float32))
+    delta = np.abs(got_bits.astype(np.int32) - want_bits.astype(np.int32))
+    assert delta.max() <= 1
+    assert (delta != 0).mean() < 2e-3
+    edge = O.bf16_bits(np.array([[0.0, 20.0, -20.0, -100.0, 2.0, 3.0, 4.0, 5.0]], np.float32))
+    out = O.bf16_to_f32_array(O.silu_mul_bf16(edge))[0]
+    assert out[0] == 0.0 and out[1] == 60.0 and abs(out[2] + 20 * np.exp(-20.0) * 4.0) < 1e-9 and out[3] == 0.0
+
+
 def test_lcg_generator_matches_reference_recurrence():
     # tests/e2e.rs:11-30: s = s*6364136223846793005 + 1442695040888963407; ((s >> 33) / u32::MAX - 0.5) * scale
     v = O.lcg_values(999, 4, 2.0)

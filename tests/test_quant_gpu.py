@@ -54,7 +54,30 @@ def test_cast_fp4_bit_exact(ctx, rows, k, groups, rule):
     assert np.array_equal(words(sf), want_sf)
 
 
+@pytest.mark.parametrize("rows,n,gran,groups,ld_pad", [
+    (128, 512, 128, 1, 0), (37, 2048, 128, 1, 0), (64, 1536, 128, 4, 64), (2048, 2048, 128, 1, 0),
+    (39, 640, 32, 3, 8), (256, 2048, 32, 1, 0),
+])
+def test_silu_mul_cast_fp8_bit_exact(ctx, rows, n, gran, groups, ld_pad):
+    # the fused kernel must give what the two reference steps give one after the other: bf16(silu(gate) * up)
+    # (moe.rs:273-296), then the FP8 quantiser on that bf16 matrix
+    ld = 2 * n + ld_pad
+    src = np.zeros((rows, ld), np.uint16)
+    src[:, :2 * n] = O.bf16_bits(O.bf16_to_f32_array(randn_bf16(rows, 2 * n, seed=rows * 3 + n + gran)) * np.float32(3.0))
+    src[0, :8] = O.bf16_bits(np.array([0.0, -0.0, 100.0, -100.0, 1e-30, -1e30, 30.0, -30.0], np.float32))
+    src[-1, n:n + 8] = O.bf16_bits(np.array([0.0, -0.0, 1e20, -1e-20, 448.0, 1.0, -1.0, 7.0], np.float32))
+    act = O.silu_mul_bf16(src[:, :2 * n].copy())
+    want_q, want_sf = O.cast_bf16_to_fp8_sf(act, n, gran, groups)
+    q, sf = dg.silu_mul_cast_fp8_sf_dev(ctx, dev(src, torch.bfloat16), ld, rows, n, gran, groups)
+    ctx.sync()
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    assert np.array_equal(words(sf), want_sf)
+
+
 def test_cast_argument_errors(ctx):
+    with pytest.raises(dg.DgError) as e:
+        dg.silu_mul_cast_fp8_sf_dev(ctx, torch.zeros((8, 1024), dtype=torch.bfloat16, device="cuda"), 512, 8, 512)   # ld < 2n
+    assert e.value.kind == "Shape"
     src = torch.zeros((8, 512), dtype=torch.bfloat16, device="cuda")
     with pytest.raises(dg.DgError) as e:
         dg.cast_bf16_to_fp8_sf_dev(ctx, src, 512, 8, 512, 64)
