@@ -206,6 +206,10 @@ class DenseWork:
                 e1.record()
                 record.append((e0, e1))
 
+    def routed_rows(self):
+        """Valid arena rows of this rank in the last step (a host read, outside any timed region)."""
+        return int(self.peer.totals[1].item()) if self.peer is not None else self.rows
+
     def e2e_setup(self):
         torch = self.torch
         self.host = []
@@ -252,8 +256,8 @@ class DenseWork:
 class MoeWork:
     """Expert-parallel contiguous grouped GEMM pair (see the module docstring)."""
 
-    def __init__(self, torch, dist, dg, ctx, dev, rank, world):
-        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel
+    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer"):
+        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel
         self.torch, self.dg, self.ctx, self.dev, self.world = torch, dg, ctx, dev, world
         c = self.c = dict(MOE)
         self.local_e = local_e = c["experts"] // world
@@ -279,14 +283,39 @@ class MoeWork:
         topw, self.topi = torch.softmax(logits, -1).topk(c["topk"], dim=-1)
         self.topw = topw.contiguous()
         self.xq, self.xsf = dg.cast_bf16_to_fp8_sf_dev(ctx, x, c["hidden"], tokens, c["hidden"], 128)
-        self.ep = ExpertParallel(c["experts"], c["topk"], DeviceRowOps(ctx))
         del x
+        # rows travel through peer memory (kernels of the library) unless the peers cannot be mapped; every rank must agree
+        self.peer, self.exchange_note = None, "nccl all_to_all_single"
+        if exchange == "peer":
+            try:
+                self.peer = PeerExpertParallel(ctx, c["experts"], c["topk"], tokens, c["hidden"], c["down_n"])
+                ok = 1
+            except dg.DgError as e:
+                ok, self.exchange_note = 0, f"nccl all_to_all_single (peer mapping failed: {e})"
+            if world > 1:
+                agreed = torch.tensor([ok], device=dev, dtype=torch.int32)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+                ok = int(agreed.item())
+            if not ok and self.peer is not None:
+                self.peer.close()
+                self.peer, self.exchange_note = None, "nccl all_to_all_single (a peer could not be mapped)"
+        if self.peer is not None:
+            cap = self.peer.capacity
+            self.exchange_note = "peer-memory stores/loads (library kernels) + count all-gather" if world > 1 else "none (local arena)"
+            self.h = torch.empty((cap, c["gate_up_n"]), dtype=torch.bfloat16, device=dev)
+            self.act = (torch.empty((cap, c["down_k"]), dtype=torch.uint8, device=dev), dg.alloc_sf(ctx, cap, c["down_k"], 128))
+        else:
+            self.ep = ExpertParallel(c["experts"], c["topk"], DeviceRowOps(ctx))
         self.w1 = dg.LpOperand(w1q, w1sf, local_e * c["gate_up_n"], c["hidden"], c["hidden"])
         self.w2 = dg.LpOperand(w2q, w2sf, local_e * c["down_n"], c["down_k"], c["down_k"])
         self.flops_per_row = 2.0 * (c["gate_up_n"] * c["hidden"] + c["down_n"] * c["down_k"])
         self.rows = 0
-        # pack, unpack, 2 x (group-end kernel, scan kernel, GEMM), SiLU-mul quantiser, combine, plus the result gather when rows travel
-        self.launches = 10 + (1 if world > 1 else 0)
+        if self.peer is not None:
+            # pair ranking, chunk scan, layout, dispatch, 2 GEMMs, SiLU-mul quantiser, combine
+            self.launches = 8
+        else:
+            # pack, unpack, 2 x (group-end kernel, scan kernel, GEMM), SiLU-mul quantiser, combine, plus the result gather when rows travel
+            self.launches = 10 + (1 if world > 1 else 0)
         self.host = None
 
     def step(self, xq=None, xsf=None, topi=None, topw=None):
@@ -295,6 +324,14 @@ class MoeWork:
         xsf = self.xsf if xsf is None else xsf
         topi = self.topi if topi is None else topi
         topw = self.topw if topw is None else topw
+        if self.peer is not None:
+            pe = self.peer
+            a_op, ends = pe.dispatch(topi, xq, xsf)
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(self.h, c["gate_up_n"]), self.local_e)
+            dg.silu_mul_cast_fp8_sf_dev(ctx, self.h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=self.act)
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, dg.LpOperand(self.act[0], self.act[1], pe.capacity, c["down_k"], c["down_k"]), ends,
+                                                          self.w2, dg.Sm100Out.Bf16(pe.result, c["down_n"]), self.local_e)
+            return pe.combine(topw)
         plan = self.ep.plan(topi)
         a, a_sf = self.ep.dispatch(plan, xq, xsf, c["hidden"])
         h = torch.empty((plan.m_pad, c["gate_up_n"]), dtype=torch.bfloat16, device=self.dev)
@@ -308,6 +345,10 @@ class MoeWork:
         out = self.ep.combine(plan, y, topw)
         self.rows, self.plan = plan.n_recv, plan
         return out
+
+    def routed_rows(self):
+        """Valid arena rows of this rank in the last step (a host read, outside any timed region)."""
+        return int(self.peer.totals[1].item()) if self.peer is not None else self.rows
 
     def e2e_setup(self):
         torch = self.torch
@@ -324,6 +365,19 @@ class MoeWork:
     def gate_up_alone(self):
         """The gate/up grouped GEMM on this rank's arena, CUDA events around the launch; returns (ms, rows)."""
         torch, dg, c = self.torch, self.dg, self.c
+        if self.peer is not None:
+            pe = self.peer
+            a_op, ends = pe.dispatch(self.topi, self.xq, self.xsf)
+            times = []
+            for _ in range(6):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(self.ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(self.h, c["gate_up_n"]), self.local_e)
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            pe.combine(self.topw)        # keeps the ranks' dispatch / combine fences paired
+            return statistics.median(times[1:]), self.routed_rows()
         plan = self.ep.plan(self.topi)
         a, a_sf = self.ep.dispatch(plan, self.xq, self.xsf, c["hidden"])
         h = torch.empty((plan.m_pad, c["gate_up_n"]), dtype=torch.bfloat16, device=self.dev)
@@ -349,6 +403,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--moe-experts", type=int, default=None, help="moe_ep: total experts (default 256); 32 gives one rank of an 8-GPU job")
+    ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
+                    help="how MoE rows travel between ranks: peer-memory kernels of the library (default) or NCCL all-to-all")
     ap.add_argument("--only", default=None, help="M,N,K: run just this dense GEMM (profiling captures); implies --workload dense_fp8")
     args = ap.parse_args()
     if args.only:
@@ -379,7 +435,7 @@ def main():
 
     # ---- build the workload (untimed): operands resident in HBM, quantised by the library's own kernels
     dense = DenseWork(torch, dg, ctx, dev, 1000 + rank) if args.workload in ("dsv3", "dense_fp8") else None
-    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world) if args.workload in ("dsv3", "moe_ep") else None
+    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep) if args.workload in ("dsv3", "moe_ep") else None
     ctx.sync()
 
     def step(record=None):
@@ -422,7 +478,7 @@ def main():
     # whole-job flops of one step: dense replicas + routed rows of all ranks
     moe_rows = 0.0
     if moe is not None:
-        r = torch.tensor([float(moe.rows)], device=dev, dtype=torch.float64)
+        r = torch.tensor([float(moe.routed_rows())], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(r, op=dist.ReduceOp.SUM)
         moe_rows = float(r.item())
@@ -508,7 +564,7 @@ def main():
             config["dense_shapes"] = DENSE_SHAPES
         if moe is not None:
             config["moe"] = dict(MOE, experts_per_gpu=moe.local_e, mk_alignment=128,
-                                 collective="nccl all_to_all_single" if world > 1 else "none")
+                                 collective=moe.exchange_note)
         launches = (dense.launches if dense is not None else 0) + (moe.launches if moe is not None else 0)
         line = {"metric": "fp8_block_scaled_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

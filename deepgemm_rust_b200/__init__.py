@@ -101,7 +101,7 @@ _sf_packed_cols = _proto("dg_sf_packed_cols", _u32, _u32, _u32)
 _sf_aligned_rows = _proto("dg_sf_aligned_rows", _u32, _u32)
 _sf_words = _proto("dg_sf_words", _sz, _u32, _u32, _u32, _u32)
 _cast_fp8 = _proto("dg_cast_bf16_to_fp8_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp)
-_silu_cast = _proto("dg_silu_mul_cast_fp8_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp)
+_silu_cast = _proto("dg_silu_mul_cast_fp8_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp)
 _cast_fp4 = _proto("dg_cast_bf16_to_fp4_packed_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, C.c_int, _vp, _vp)
 _transform_sf = _proto("dg_transform_sf", C.c_int, _vp, _vp, _u32, _u32, _u32, _vp)
 _tsf1d = _proto("dg_transform_sf1d_packed_ue8m0", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp)
@@ -113,6 +113,16 @@ _gather_rows = _proto("dg_gather_rows", C.c_int, _vp, _vp, _sz, _vp, _u32, _u32,
 _moe_pack = _proto("dg_moe_pack_rows", C.c_int, _vp, _vp, _u32, _vp, _u32, _u32, _vp, _u32, _vp, _sz)
 _moe_unpack = _proto("dg_moe_unpack_rows", C.c_int, _vp, _vp, _sz, _u32, _u32, _vp, _u32, _vp, _vp, _u32)
 _moe_combine = _proto("dg_moe_combine", C.c_int, _vp, _vp, _sz, _vp, _vp, _u32, _u32, _u32, _vp, _sz)
+_peer_alloc = _proto("dg_peer_alloc", C.c_int, _vp, _sz, C.POINTER(_vp), C.c_char_p)
+_peer_open = _proto("dg_peer_open", C.c_int, _vp, C.c_char_p, C.POINTER(_vp))
+_peer_close = _proto("dg_peer_close", C.c_int, _vp, _vp)
+_peer_free = _proto("dg_peer_free", C.c_int, _vp, _vp)
+_ep_hist_words = _proto("dg_ep_block_hist_words", _sz, _u32, _u32)
+_ep_count = _proto("dg_ep_count", C.c_int, _vp, _vp, _u32, _u32, _vp, _vp, _vp)
+_ep_layout = _proto("dg_ep_layout", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp)
+_ep_dispatch = _proto("dg_ep_dispatch", C.c_int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _u32, _u32, _vp, _vp, _u32,
+                      _u32, _vp)
+_ep_combine = _proto("dg_ep_combine", C.c_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _sz, _u32, _vp, _sz)
 _expire_wait = _proto("dg_debug_expire_wait", C.c_int, _vp, _u32)
 _set_mk = _proto("dg_set_mk_alignment_for_contiguous_layout", C.c_int, _u32)
 _get_mk = _proto("dg_get_mk_alignment_for_contiguous_layout", _u32)
@@ -347,13 +357,19 @@ def cast_bf16_to_fp8_sf_dev(ctx, src: torch.Tensor, src_ld: int, rows: int, k: i
     return dst, sf
 
 
-def silu_mul_cast_fp8_sf_dev(ctx, gate_up: torch.Tensor, src_ld: int, rows: int, n: int, gran_k: int = 128, num_groups: int = 1
-                             ) -> Tuple[torch.Tensor, torch.Tensor]:
+def silu_mul_cast_fp8_sf_dev(ctx, gate_up: torch.Tensor, src_ld: int, rows: int, n: int, gran_k: int = 128, num_groups: int = 1,
+                             live_rows: Optional[torch.Tensor] = None, out=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """moe.rs:273-296 (silu(gate) * up on a (rows, 2n) bf16 matrix) fused with the FP8 quantiser of the
-    activation: returns (e4m3 bytes (rows, n), packed UE8M0 words) ready to be the next grouped GEMM's A."""
-    dst = torch.empty((rows, n), dtype=torch.uint8, device=gate_up.device)
-    sf = alloc_sf(ctx, rows, n, gran_k, num_groups)
-    _check(_silu_cast(ctx._h, _vp(gate_up.data_ptr()), src_ld, rows, n, gran_k, num_groups, _vp(dst.data_ptr()), _vp(sf.data_ptr())))
+    activation: returns (e4m3 bytes (rows, n), packed UE8M0 words) ready to be the next grouped GEMM's A.
+    live_rows: optional device word (uint32/int32 tensor); rows from its value on are left unwritten.
+    out: optional (bytes, scale words) tensors to write instead of new ones."""
+    if out is not None:
+        dst, sf = out
+    else:
+        dst = torch.empty((rows, n), dtype=torch.uint8, device=gate_up.device)
+        sf = alloc_sf(ctx, rows, n, gran_k, num_groups)
+    _check(_silu_cast(ctx._h, _vp(gate_up.data_ptr()), src_ld, rows, n, gran_k, num_groups, _vp(dst.data_ptr()), _vp(sf.data_ptr()),
+                      _vp(live_rows.data_ptr()) if live_rows is not None else _vp()))
     return dst, sf
 
 
@@ -445,6 +461,70 @@ def moe_combine_dev(ctx, rows: torch.Tensor, pos: torch.Tensor, weights: torch.T
     _check(_moe_combine(ctx._h, _vp(rows.data_ptr()), rows.stride(0), _vp(pos.data_ptr()), _vp(weights.data_ptr()), tokens, topk, n,
                         _vp(out.data_ptr()), out.stride(0)))
     return out
+
+
+PEER_HANDLE_BYTES = 64
+
+
+def peer_alloc(ctx, nbytes: int, export: bool = True) -> Tuple[int, bytes]:
+    """A device buffer other processes on this node can map: (address, 64-byte handle to send them;
+    empty when export is False, for a buffer nobody else will map)."""
+    ptr, handle = _vp(), C.create_string_buffer(PEER_HANDLE_BYTES)
+    _check(_peer_alloc(ctx._h, nbytes, C.byref(ptr), handle if export else None))
+    return ptr.value, (handle.raw if export else b"")
+
+
+def peer_open(ctx, handle: bytes) -> int:
+    ptr = _vp()
+    _check(_peer_open(ctx._h, C.create_string_buffer(bytes(handle), PEER_HANDLE_BYTES), C.byref(ptr)))
+    return ptr.value
+
+
+def peer_close(ctx, ptr: int):
+    _check(_peer_close(ctx._h, _vp(ptr)))
+
+
+def peer_free(ctx, ptr: int):
+    _check(_peer_free(ctx._h, _vp(ptr)))
+
+
+class _RawDeviceArray:
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def tensor_from_ptr(ptr: int, shape, dtype: torch.dtype, ordinal: int) -> torch.Tensor:
+    """A torch view of device memory this library allocated (no copy; the caller keeps the memory alive)."""
+    if dtype == torch.bfloat16:     # the array interface has no bf16: view 16-bit words
+        return torch.as_tensor(_RawDeviceArray(ptr, shape, "<i2"), device=f"cuda:{ordinal}").view(torch.bfloat16)
+    typestr = {torch.uint8: "|u1", torch.int32: "<i4", torch.int64: "<i8", torch.float32: "<f4"}[dtype]
+    return torch.as_tensor(_RawDeviceArray(ptr, shape, typestr), device=f"cuda:{ordinal}")
+
+
+def ep_block_hist_words(pairs: int, num_experts: int) -> int:
+    return _ep_hist_words(pairs, num_experts)
+
+
+def ep_count_dev(ctx, expert_of_pair, pairs, num_experts, local_rank, block_hist, counts):
+    _check(_ep_count(ctx._h, _vp(expert_of_pair.data_ptr()), pairs, num_experts, _vp(local_rank.data_ptr()), _vp(block_hist.data_ptr()),
+                     _vp(counts.data_ptr())))
+
+
+def ep_layout_dev(ctx, all_counts, world, rank, num_experts, alignment, capacity, pair_base, group_ends, totals):
+    _check(_ep_layout(ctx._h, _vp(all_counts.data_ptr()), world, rank, num_experts, alignment, capacity, _vp(pair_base.data_ptr()),
+                      _vp(group_ends.data_ptr()), _vp(totals.data_ptr())))
+
+
+def ep_dispatch_dev(ctx, expert_of_pair, local_rank, block_base, pair_base, pairs, topk, num_experts, world, data, k, sf, sf_stride, sf_cols,
+                    peer_data, peer_sf, peer_sf_stride, capacity, pos_of_pair):
+    _check(_ep_dispatch(ctx._h, _vp(expert_of_pair.data_ptr()), _vp(local_rank.data_ptr()), _vp(block_base.data_ptr()),
+                        _vp(pair_base.data_ptr()), pairs, topk, num_experts, world, _vp(data.data_ptr()), k, _vp(sf.data_ptr()), sf_stride,
+                        sf_cols, _vp(peer_data.data_ptr()), _vp(peer_sf.data_ptr()), peer_sf_stride, capacity, _vp(pos_of_pair.data_ptr())))
+
+
+def ep_combine_dev(ctx, expert_of_pair, pos_of_pair, weights, tokens, topk, num_experts, world, peer_rows, pitch, n, out, out_pitch):
+    _check(_ep_combine(ctx._h, _vp(expert_of_pair.data_ptr()), _vp(pos_of_pair.data_ptr()), _vp(weights.data_ptr()), tokens, topk,
+                       num_experts, world, _vp(peer_rows.data_ptr()), pitch, n, _vp(out.data_ptr()), out_pitch))
 
 
 def debug_expire_wait(ctx, limit_us: int = 1000):

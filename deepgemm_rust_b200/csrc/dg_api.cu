@@ -755,7 +755,7 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous_static(int device, void* cuda_stream, c
 
 // ------------------------------------------------------------------ quantise / re-layout
 static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t gran, uint32_t groups, int rule,
-                       bool fp4, uint8_t* dst, uint32_t* sf, bool silu_mul = false) {
+                       bool fp4, uint8_t* dst, uint32_t* sf, bool silu_mul = false, const uint32_t* live_rows = nullptr) {
     if (!ctx || !src || !dst || !sf) return fail(DG_ERR_SHAPE, "null argument");
     if (groups == 0) groups = 1;
     if (rows % groups != 0) return fail(DG_ERR_SHAPE, "rows (%u) must be a multiple of num_groups (%u)", rows, groups);
@@ -770,6 +770,7 @@ static int cast_common(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32
     p.sf_cols = dg_sf_packed_cols(k, gran);
     p.sf_stride = align4(rows / groups);
     p.rule = rule;
+    p.live_rows = live_rows;
     // one block per 8 consecutive rows x one 1024-element segment (one warp per row)
     const uint64_t units = static_cast<uint64_t>(ceil_div(rows, 8)) * ceil_div(k, 1024);
     if (units > 0x7FFFFFFFull) return fail(DG_ERR_SHAPE, "matrix too large for one launch");
@@ -792,10 +793,10 @@ int dg_cast_bf16_to_fp8_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, ui
 }
 
 int dg_silu_mul_cast_fp8_sf(dg_ctx* ctx, const uint16_t* gate_up, uint32_t src_ld, uint32_t rows, uint32_t n, uint32_t gran_k,
-                            uint32_t num_groups, uint8_t* dst, uint32_t* sf) {
+                            uint32_t num_groups, uint8_t* dst, uint32_t* sf, const uint32_t* live_rows) {
     if (gran_k != 32 && gran_k != 128) return fail(DG_ERR_SHAPE, "gran_k must be 32 or 128");
     if (n == 0 || n % (gran_k * 4) != 0) return fail(DG_ERR_SHAPE, "n must be a multiple of %u for gran %u", gran_k * 4, gran_k);
-    return cast_common(ctx, gate_up, src_ld, rows, n, gran_k, num_groups, 0, false, dst, sf, true);
+    return cast_common(ctx, gate_up, src_ld, rows, n, gran_k, num_groups, 0, false, dst, sf, true, live_rows);
 }
 
 int dg_cast_bf16_to_fp4_packed_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
@@ -929,6 +930,124 @@ int dg_moe_combine(dg_ctx* ctx, const uint16_t* rows, size_t pitch, const int32_
     const uint64_t threads = static_cast<uint64_t>(tokens) * (n / 8);
     dg::dg_moe_combine_kernel<<<static_cast<uint32_t>((threads + 255) / 256), 256, 0, ctx->stream>>>(rows, pitch, pos, weights, tokens, topk, n, out,
                                                                                                     out_pitch);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Buffers other processes' GPUs can map, and the expert-parallel exchange over them
+// ------------------------------------------------------------------------------------------------
+int dg_peer_alloc(dg_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle64) {
+    if (!ctx || !ptr || bytes == 0) return fail(DG_ERR_SHAPE, "null argument or zero size");
+    static_assert(sizeof(cudaIpcMemHandle_t) == DG_PEER_HANDLE_BYTES, "handle size");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    void* p = nullptr;
+    DG_CUDA(cudaMalloc(&p, bytes));
+    if (handle64 != nullptr) {
+        cudaIpcMemHandle_t h;
+        const cudaError_t e = cudaIpcGetMemHandle(&h, p);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            return fail(DG_ERR_DRIVER, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+        }
+        memcpy(handle64, &h, sizeof(h));
+    }
+    *ptr = p;
+    return DG_OK;
+}
+
+int dg_peer_open(dg_ctx* ctx, const unsigned char* handle64, void** ptr) {
+    if (!ctx || !ptr || !handle64) return fail(DG_ERR_SHAPE, "null argument");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    DG_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return DG_OK;
+}
+
+int dg_peer_close(dg_ctx* ctx, void* ptr) {
+    if (!ctx || !ptr) return fail(DG_ERR_SHAPE, "null argument");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    DG_CUDA(cudaIpcCloseMemHandle(ptr));
+    return DG_OK;
+}
+
+int dg_peer_free(dg_ctx* ctx, void* ptr) {
+    if (!ctx || !ptr) return fail(DG_ERR_SHAPE, "null argument");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    DG_CUDA(cudaFree(ptr));
+    return DG_OK;
+}
+
+size_t dg_ep_block_hist_words(uint32_t pairs, uint32_t num_experts) {
+    return static_cast<size_t>(ceil_div(pairs, dg::kEpChunk)) * num_experts;
+}
+
+int dg_ep_count(dg_ctx* ctx, const int32_t* expert_of_pair, uint32_t pairs, uint32_t num_experts, int32_t* local_rank, uint32_t* block_hist,
+                uint32_t* counts) {
+    if (!ctx || !expert_of_pair || !local_rank || !block_hist || !counts) return fail(DG_ERR_SHAPE, "null argument");
+    if (num_experts == 0 || num_experts > 8192) return fail(DG_ERR_SHAPE, "num_experts must be in [1, 8192]");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    const uint32_t chunks = ceil_div(pairs, dg::kEpChunk);
+    if (chunks > 0)
+        dg::dg_ep_rank_pairs_kernel<<<chunks, dg::kEpChunk, num_experts * sizeof(uint32_t), ctx->stream>>>(expert_of_pair, pairs, num_experts,
+                                                                                                         local_rank, block_hist);
+    dg::dg_ep_block_scan_kernel<<<ceil_div(num_experts, 256), 256, 0, ctx->stream>>>(block_hist, chunks, num_experts, counts);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32_t rank, uint32_t num_experts, uint32_t alignment,
+                 uint32_t capacity, uint32_t* pair_base, uint32_t* group_ends, uint32_t* totals) {
+    if (!ctx || !all_counts || !pair_base || !group_ends || !totals) return fail(DG_ERR_SHAPE, "null argument");
+    if (world == 0 || world > 1024 || rank >= world || num_experts == 0 || num_experts > 4096 || num_experts % world != 0)
+        return fail(DG_ERR_SHAPE, "need 1 <= world <= 1024, rank < world, num_experts <= 4096 and a multiple of world");
+    if (alignment == 0) return fail(DG_ERR_SHAPE, "alignment must be positive");
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_ep_layout_kernel<<<1, 1024, 3 * num_experts * sizeof(uint32_t), ctx->stream>>>(all_counts, world, rank, num_experts, alignment, capacity,
+                                                                                         pair_base, group_ends, totals);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* local_rank, const uint32_t* block_base, const uint32_t* pair_base,
+                   uint32_t pairs, uint32_t topk, uint32_t num_experts, uint32_t world, const uint8_t* data, uint32_t k, const uint32_t* sf,
+                   uint32_t sf_stride, uint32_t sf_cols, void* const* peer_data, void* const* peer_sf, uint32_t peer_sf_stride,
+                   uint32_t capacity, int32_t* pos_of_pair) {
+    if (!ctx || !expert_of_pair || !local_rank || !block_base || !pair_base || !data || !sf || !peer_data || !peer_sf || !pos_of_pair)
+        return fail(DG_ERR_SHAPE, "null argument");
+    if (k % 16 || !aligned16(data)) return fail(DG_ERR_SHAPE, "k and the token rows must be multiples of 16 bytes");
+    if (topk == 0 || pairs % topk != 0) return fail(DG_ERR_SHAPE, "pairs (%u) must be tokens x topk (%u)", pairs, topk);
+    if (world == 0 || num_experts % world != 0) return fail(DG_ERR_SHAPE, "num_experts (%u) must be a multiple of world (%u)", num_experts, world);
+    if (peer_sf_stride < capacity) return fail(DG_ERR_SHAPE, "arena scale stride smaller than the arena capacity");
+    if (pairs == 0) return DG_OK;
+    dg::EpDispatchParams p;
+    p.expert_of_pair = expert_of_pair; p.local_rank = local_rank; p.block_base = block_base; p.pair_base = pair_base;
+    p.data = data; p.sf = sf;
+    p.peer_data = reinterpret_cast<uint8_t* const*>(peer_data); p.peer_sf = reinterpret_cast<uint32_t* const*>(peer_sf);
+    p.pos_of_pair = pos_of_pair;
+    p.pairs = pairs; p.topk = topk; p.k = k; p.sf_cols = sf_cols; p.sf_stride = sf_stride; p.peer_sf_stride = peer_sf_stride;
+    p.num_experts = num_experts; p.experts_per_rank = num_experts / world; p.capacity = capacity;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    dg::dg_ep_dispatch_kernel<<<ceil_div(pairs, 8), 256, 0, ctx->stream>>>(p);
+    DG_CUDA(cudaGetLastError());
+    return DG_OK;
+}
+
+int dg_ep_combine(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* pos_of_pair, const float* weights, uint32_t tokens, uint32_t topk,
+                  uint32_t num_experts, uint32_t world, const void* const* peer_rows, size_t pitch, uint32_t n, uint16_t* out, size_t out_pitch) {
+    if (!ctx || !expert_of_pair || !pos_of_pair || !weights || !peer_rows || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (n % 8 || pitch % 8 || out_pitch % 8 || !aligned16(out)) return fail(DG_ERR_SHAPE, "n and pitches must be multiples of 8 elements");
+    if (world == 0 || num_experts % world != 0) return fail(DG_ERR_SHAPE, "num_experts (%u) must be a multiple of world (%u)", num_experts, world);
+    if (tokens == 0 || n == 0) return DG_OK;
+    dg::EpCombineParams p;
+    p.expert_of_pair = expert_of_pair; p.pos_of_pair = pos_of_pair; p.weights = weights;
+    p.peer_rows = reinterpret_cast<const uint16_t* const*>(peer_rows);
+    p.out = out; p.pitch = pitch; p.out_pitch = out_pitch;
+    p.tokens = tokens; p.topk = topk; p.n = n; p.experts_per_rank = num_experts / world;
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    const uint64_t threads = static_cast<uint64_t>(tokens) * (n / 8);
+    dg::dg_ep_combine_kernel<<<static_cast<uint32_t>((threads + 255) / 256), 256, 0, ctx->stream>>>(p);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }

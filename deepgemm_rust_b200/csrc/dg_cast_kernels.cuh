@@ -57,6 +57,7 @@ struct CastParams {
     uint32_t* sf;          // packed scale words
     uint32_t src_ld, rows, k, group_rows, sf_cols, sf_stride;
     int rule;
+    const uint32_t* live_rows;   // optional device word: rows at or beyond it are skipped (a row count only the device knows)
 };
 
 // One warp quantises 1024 consecutive K elements of one row: four 16-byte loads per lane, all issued
@@ -74,6 +75,7 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
     const uint32_t lane = threadIdx.x % 32, warp = threadIdx.x / 32;
     const uint32_t segs_per_row = (p.k + kSeg - 1) / kSeg;
     const uint32_t seg = blockIdx.x % segs_per_row, row0 = (blockIdx.x / segs_per_row) * 8;
+    if (p.live_rows != nullptr && row0 >= __ldg(p.live_rows)) return;   // the same for the whole block
     const uint32_t row = row0 + warp;
     const bool live = row < p.rows;
     const uint16_t* src_row = p.src + static_cast<size_t>(live ? row : 0) * p.src_ld;

@@ -92,4 +92,202 @@ __global__ void __launch_bounds__(256) dg_moe_combine_kernel(const uint16_t* __r
     reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * out_pitch)[c] = o;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Expert-parallel exchange over peer memory.  Every rank owns num_experts / world consecutive
+// experts and exposes three buffers to its peers: the group-contiguous arena (e4m3 rows), the
+// arena's packed scale words, and the result rows of its last grouped GEMM.  A step:
+//   rank pairs    stable position of every (token, j) pair among this rank's pairs for its expert
+//   block scan    per-expert totals of this rank (exchanged with a small all-gather)
+//   layout        from all ranks' totals: where each expert's group starts on its owner, where this
+//                 rank's rows go inside it, and the owner's group-end table for the grouped GEMM
+//   dispatch      every pair's row and scale words are written straight to their arena row on the
+//                 owner (plain stores to peer memory; no send buffer, no unpack pass)
+//   combine       every token reads its topk result rows from the owners' result buffers and
+//                 reduces them (plain loads from peer memory; no gather pass, no receive buffer)
+// Cross-rank ordering (arena complete before the GEMM reads it, results complete before the
+// combine reads them) is the host's job: a collective on the same stream between the steps.
+// None of these kernels waits on another rank.
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t kEpChunk = 256;   // pairs per block of the ranking kernel
+
+// local_rank[p] = number of earlier pairs of the same chunk with the same expert;
+// block_hist[b * num_experts + e] = pairs of chunk b routed to expert e.  Expert ids outside
+// [0, num_experts) are dropped (rank -1): such a pair is neither sent nor reduced.
+__global__ void __launch_bounds__(kEpChunk) dg_ep_rank_pairs_kernel(const int32_t* __restrict__ expert_of_pair, uint32_t pairs, uint32_t num_experts,
+                                                                    int32_t* __restrict__ local_rank, uint32_t* __restrict__ block_hist) {
+    extern __shared__ uint32_t ep_hist[];
+    __shared__ int32_t ids[kEpChunk];
+    const uint32_t tid = threadIdx.x, p = blockIdx.x * kEpChunk + tid;
+    int32_t e = p < pairs ? __ldg(expert_of_pair + p) : -1;
+    if (e < 0 || static_cast<uint32_t>(e) >= num_experts) e = -1;
+    ids[tid] = e;
+    for (uint32_t i = tid; i < num_experts; i += kEpChunk) ep_hist[i] = 0;
+    __syncthreads();
+    int32_t rank = 0;
+    for (uint32_t j = 0; j < tid; ++j) rank += ids[j] == e ? 1 : 0;
+    if (e >= 0) atomicAdd(&ep_hist[e], 1u);
+    if (p < pairs) local_rank[p] = e >= 0 ? rank : -1;
+    __syncthreads();
+    for (uint32_t i = tid; i < num_experts; i += kEpChunk) block_hist[static_cast<size_t>(blockIdx.x) * num_experts + i] = ep_hist[i];
+}
+
+// Exclusive scan over chunks, per expert, in place; counts[e] = this rank's pairs for expert e.
+__global__ void __launch_bounds__(256) dg_ep_block_scan_kernel(uint32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_t num_experts,
+                                                               uint32_t* __restrict__ counts) {
+    const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= num_experts) return;
+    uint32_t running = 0;
+    for (uint32_t b = 0; b < num_blocks; ++b) {
+        const size_t at = static_cast<size_t>(b) * num_experts + e;
+        const uint32_t v = block_hist[at];
+        block_hist[at] = running;
+        running += v;
+    }
+    counts[e] = running;
+}
+
+// all_counts: (world, num_experts) pairs per source rank and expert.  One block.
+//   pair_base[e]   arena row (on the owner of e) of this rank's first pair for expert e
+//   group_ends[l]  one past the last valid arena row of local expert l (the grouped GEMM's table)
+//   totals[0..3]   arena rows in use on this rank (groups padded to `alignment`), valid rows on this
+//                  rank, 1 if any owner's arena would exceed `capacity` rows (dispatch then drops the
+//                  rows that do not fit), largest arena in use on any rank
+__global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __restrict__ all_counts, uint32_t world, uint32_t rank, uint32_t num_experts,
+                                                            uint32_t alignment, uint32_t capacity, uint32_t* __restrict__ pair_base,
+                                                            uint32_t* __restrict__ group_ends, uint32_t* __restrict__ totals) {
+    extern __shared__ uint32_t ep_smem[];
+    uint32_t* rows_of = ep_smem;                  // [num_experts] rows of the expert over all source ranks
+    uint32_t* before_me = ep_smem + num_experts;  // [num_experts] rows from lower source ranks
+    uint32_t* start_of = ep_smem + 2 * num_experts;
+    __shared__ uint32_t arena_rows[1024];
+    const uint32_t local = num_experts / world;
+    for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) {
+        uint32_t total = 0, before = 0;
+        for (uint32_t s = 0; s < world; ++s) {
+            const uint32_t c = __ldg(all_counts + static_cast<size_t>(s) * num_experts + e);
+            if (s < rank) before += c;
+            total += c;
+        }
+        rows_of[e] = total;
+        before_me[e] = before;
+    }
+    __syncthreads();
+    for (uint32_t owner = threadIdx.x; owner < world; owner += blockDim.x) {
+        uint32_t row = 0, valid = 0;
+        for (uint32_t l = 0; l < local; ++l) {
+            const uint32_t e = owner * local + l;
+            start_of[e] = row;
+            if (owner == rank) group_ends[l] = row + rows_of[e];
+            valid += rows_of[e];
+            row += (rows_of[e] + alignment - 1) / alignment * alignment;
+        }
+        arena_rows[owner] = row;
+        if (owner == rank) { totals[0] = row; totals[1] = valid; }
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) pair_base[e] = start_of[e] + before_me[e];
+    if (threadIdx.x == 0) {
+        uint32_t largest = 0;
+        for (uint32_t s = 0; s < world; ++s) largest = arena_rows[s] > largest ? arena_rows[s] : largest;
+        totals[2] = largest > capacity ? 1u : 0u;
+        totals[3] = largest;
+    }
+}
+
+struct EpDispatchParams {
+    const int32_t* expert_of_pair;   // (pairs)
+    const int32_t* local_rank;       // (pairs)
+    const uint32_t* block_base;      // (chunks, num_experts) exclusive scan of the chunk histograms
+    const uint32_t* pair_base;       // (num_experts)
+    const uint8_t* data;             // (tokens, k) e4m3 rows of this rank's tokens
+    const uint32_t* sf;              // packed scale words sf[c * sf_stride + token]
+    uint8_t* const* peer_data;       // [world] arena of each rank, (capacity, k)
+    uint32_t* const* peer_sf;        // [world] arena scale words, sf[c * peer_sf_stride + row]
+    int32_t* pos_of_pair;            // (pairs) arena row on the owner, -1 if dropped
+    uint32_t pairs, topk, k, sf_cols, sf_stride, peer_sf_stride, num_experts, experts_per_rank, capacity;
+};
+
+// One warp per (token, j) pair.
+__global__ void __launch_bounds__(256) dg_ep_dispatch_kernel(const EpDispatchParams p) {
+    const uint32_t lane = threadIdx.x % 32;
+    const uint64_t pair = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    if (pair >= p.pairs) return;
+    const int32_t lr = __ldg(p.local_rank + pair);
+    if (lr < 0) { if (lane == 0) p.pos_of_pair[pair] = -1; return; }
+    const uint32_t e = static_cast<uint32_t>(__ldg(p.expert_of_pair + pair));
+    const uint32_t row = __ldg(p.pair_base + e) + __ldg(p.block_base + (pair / kEpChunk) * p.num_experts + e) + static_cast<uint32_t>(lr);
+    if (row >= p.capacity) { if (lane == 0) p.pos_of_pair[pair] = -1; return; }
+    if (lane == 0) p.pos_of_pair[pair] = static_cast<int32_t>(row);
+    const uint32_t owner = e / p.experts_per_rank, tok = static_cast<uint32_t>(pair / p.topk);
+    const uint4* src = reinterpret_cast<const uint4*>(p.data + static_cast<size_t>(tok) * p.k);
+    uint4* dst = reinterpret_cast<uint4*>(p.peer_data[owner] + static_cast<size_t>(row) * p.k);
+    const uint32_t vecs = p.k / 16;
+    uint32_t c = lane;
+    for (; c + 96 < vecs; c += 128) {      // four loads in flight per lane
+        const uint4 v0 = __ldg(src + c), v1 = __ldg(src + c + 32), v2 = __ldg(src + c + 64), v3 = __ldg(src + c + 96);
+        dst[c] = v0; dst[c + 32] = v1; dst[c + 64] = v2; dst[c + 96] = v3;
+    }
+    for (; c < vecs; c += 32) dst[c] = __ldg(src + c);
+    uint32_t* dsf = p.peer_sf[owner];
+    for (uint32_t w = lane; w < p.sf_cols; w += 32)
+        dsf[static_cast<size_t>(w) * p.peer_sf_stride + row] = __ldg(p.sf + static_cast<size_t>(w) * p.sf_stride + tok);
+}
+
+struct EpCombineParams {
+    const int32_t* expert_of_pair;    // (tokens, topk)
+    const int32_t* pos_of_pair;       // (tokens, topk) result row on the owner, < 0 skips the term
+    const float* weights;             // (tokens, topk)
+    const uint16_t* const* peer_rows; // [world] bf16 result rows of each rank, (capacity, pitch)
+    uint16_t* out;                    // (tokens, out_pitch) bf16
+    size_t pitch, out_pitch;
+    uint32_t tokens, topk, n, experts_per_rank;
+};
+
+// out[t, :] = bf16( sum_j w[t, j] * rows_of_owner(t, j)[pos[t, j], :] ): the same ordered fused multiply-add
+// chain as dg_moe_combine_kernel, reading each term from the rank that computed it.  One thread owns 8 columns.
+__global__ void __launch_bounds__(256) dg_ep_combine_kernel(const EpCombineParams p) {
+    const uint32_t chunks = p.n / 8;
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<uint64_t>(p.tokens) * chunks) return;
+    const uint32_t t = static_cast<uint32_t>(i / chunks), c = static_cast<uint32_t>(i % chunks);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (uint32_t j0 = 0; j0 < p.topk; j0 += 4) {
+        // up to four independent peer loads in flight before the first use
+        uint4 v[4];
+        float wj[4];
+        bool live[4];
+        #pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            const uint32_t j = j0 + u;
+            live[u] = false;
+            if (j < p.topk) {
+                const size_t at = static_cast<size_t>(t) * p.topk + j;
+                const int32_t row = __ldg(p.pos_of_pair + at);
+                if (row >= 0) {
+                    const uint32_t owner = static_cast<uint32_t>(__ldg(p.expert_of_pair + at)) / p.experts_per_rank;
+                    live[u] = true;
+                    wj[u] = __ldg(p.weights + at);
+                    v[u] = *(reinterpret_cast<const uint4*>(p.peer_rows[owner] + static_cast<size_t>(row) * p.pitch) + c);
+                }
+            }
+        }
+        #pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            if (!live[u]) continue;
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+            #pragma unroll
+            for (uint32_t q = 0; q < 4; ++q) {
+                acc[2 * q] = fmaf(wj[u], __uint_as_float(w[q] << 16), acc[2 * q]);
+                acc[2 * q + 1] = fmaf(wj[u], __uint_as_float(w[q] & 0xFFFF0000u), acc[2 * q + 1]);
+            }
+        }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.out_pitch)[c] = o;
+}
+
 }  // namespace dg

@@ -13,7 +13,12 @@ Rank r owns experts [r*E/W, (r+1)*E/W); its weights never move.  A step:
   compute   the caller's grouped GEMMs on the arena
   combine   gather result rows in arrival order, all_to_all_single back, weighted sum per token
 
-The index arithmetic is plain torch and runs on any device (the CPU tests drive it with gloo); the row
+`PeerExpertParallel` is the same step without the collectives' staging: every rank maps its peers' arenas and
+result buffers, dispatch writes each row straight into its arena row on the owner and combine reads each
+result row straight from the owner (kernels of this library, plain stores/loads over NVLink); the only
+collectives left are an all-gather of the per-expert counts and two one-word all-reduces that order the ranks.
+
+`ExpertParallel`'s index arithmetic is plain torch and runs on any device (the CPU tests drive it with gloo); the row
 movers come from the `ops` object: `DeviceRowOps` (CUDA kernels of this library, the only one shipped).
 """
 from dataclasses import dataclass
@@ -136,3 +141,130 @@ class ExpertParallel:
         back = self.ops.gather(y, plan.dst_pos, plan.n_recv)
         home = self._exchange(back, plan.pairs, plan.send_splits, plan.recv_splits)
         return self.ops.combine(home, plan.pos_of_pair, weights)
+
+
+class PeerExpertParallel:
+    """Expert-parallel dispatch / combine over peer memory.  One instance per rank and per layer shape.
+
+    capacity: arena rows every rank provides.  The default is the worst case (all pairs of all ranks routed to
+    one rank), so no routing can overflow; a smaller value saves memory, and a step that would overflow it drops
+    the rows that do not fit and reports it through `overflowed()`.
+    Alignment-padding rows of the arena are never written (they hold zeros until a longer group has used them, then
+    stale rows); the grouped GEMM computes them inside its tiles and stores none of them.
+    Nothing in a step reads back to the host: the arena's row count stays on the device (`totals`), the grouped
+    GEMMs take `group_ends`, and operands are declared with `capacity` rows.
+    """
+
+    def __init__(self, ctx, num_experts: int, topk: int, max_tokens: int, hidden: int, out_n: int, gran: int = 128,
+                 group: Optional[dist.ProcessGroup] = None, alignment: int = 128, capacity: Optional[int] = None):
+        import deepgemm_rust_b200 as dg
+        self.dg, self.ctx, self.group = dg, ctx, group
+        self.distributed = dist.is_available() and dist.is_initialized() and (group is not None or dist.get_world_size() > 1)
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        if num_experts % self.world != 0:
+            raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
+        self.num_experts, self.local_experts, self.topk = num_experts, num_experts // self.world, topk
+        self.max_pairs, self.hidden, self.out_n, self.gran, self.alignment = max_tokens * topk, hidden, out_n, gran, alignment
+        worst = self.world * self.max_pairs + alignment * self.local_experts
+        cap = min(capacity, worst) if capacity else worst
+        self.capacity = cap = (cap + 127) // 128 * 128
+        self.sf_cols, self.sf_stride = dg.sf_packed_cols(hidden, gran), dg.sf_aligned_rows(cap)
+        dev = self.device = torch.device(f"cuda:{ctx.ordinal}")
+
+        def region(nbytes):
+            return (nbytes + 255) // 256 * 256
+        sizes = [region(cap * hidden), region(self.sf_cols * self.sf_stride * 4), region(cap * out_n * 2)]
+        offs = [0, sizes[0], sizes[0] + sizes[1]]
+        self._base, handle = dg.peer_alloc(ctx, sum(sizes), export=self.distributed)
+        self._opened = []
+        bases = [self._base]
+        if self.distributed:
+            mine = torch.frombuffer(bytearray(handle), dtype=torch.uint8).to(dev)
+            every = torch.empty((self.world, dg.PEER_HANDLE_BYTES), dtype=torch.uint8, device=dev)
+            dist.all_gather_into_tensor(every, mine, group=group)
+            every = every.cpu().numpy()
+            bases = []
+            for r in range(self.world):
+                if r == self.rank:
+                    bases.append(self._base)
+                else:
+                    bases.append(dg.peer_open(ctx, every[r].tobytes()))
+                    self._opened.append(bases[-1])
+        self._peer_data = torch.tensor([b + offs[0] for b in bases], dtype=torch.int64, device=dev)
+        self._peer_sf = torch.tensor([b + offs[1] for b in bases], dtype=torch.int64, device=dev)
+        self._peer_rows = torch.tensor([b + offs[2] for b in bases], dtype=torch.int64, device=dev)
+        self.arena = dg.tensor_from_ptr(self._base + offs[0], (cap, hidden), torch.uint8, ctx.ordinal)
+        self.arena_sf = dg.tensor_from_ptr(self._base + offs[1], (self.sf_cols * self.sf_stride,), torch.int32, ctx.ordinal)
+        self.result = dg.tensor_from_ptr(self._base + offs[2], (cap, out_n), torch.bfloat16, ctx.ordinal)
+        self.arena.zero_()
+        self.arena_sf.zero_()
+        i32 = dict(dtype=torch.int32, device=dev)
+        self._local_rank = torch.empty(self.max_pairs, **i32)
+        self._block_hist = torch.empty(dg.ep_block_hist_words(self.max_pairs, num_experts), **i32)
+        self._counts = torch.empty(num_experts, **i32)
+        self._all_counts = torch.empty((self.world, num_experts), **i32) if self.distributed else self._counts.view(1, -1)
+        self._pair_base = torch.empty(num_experts, **i32)
+        self.group_ends = torch.empty(self.local_experts, **i32)
+        self.totals = torch.zeros(4, **i32)          # arena rows in use, valid rows, overflow flag, largest arena
+        self.pos_of_pair = torch.empty(self.max_pairs, **i32)
+        self._fence_word = torch.zeros(1, **i32)
+        self._experts = None
+        self._tokens = 0
+        self._fence()                                 # every rank's buffers are mapped and cleared before the first step
+
+    def _fence(self):
+        """Orders the ranks on the stream: what each wrote before is visible to all after."""
+        if self.distributed:
+            dist.all_reduce(self._fence_word, group=self.group)
+
+    def operand(self):
+        """The arena as the grouped GEMMs' A: `capacity` rows, of which the group table bounds the work."""
+        return self.dg.LpOperand(self.arena, self.arena_sf, self.capacity, self.hidden, self.hidden, 8, self.gran)
+
+    def dispatch(self, topk_idx: torch.Tensor, xq: torch.Tensor, xsf: torch.Tensor):
+        """This rank's e4m3 token rows + packed scales -> arena rows on the expert ranks.  Returns (operand, group_ends)."""
+        dg, ctx = self.dg, self.ctx
+        tokens, topk = topk_idx.shape
+        pairs = tokens * topk
+        if topk != self.topk or pairs > self.max_pairs:
+            raise ValueError(f"routing of shape {tuple(topk_idx.shape)} exceeds what this exchange was built for")
+        self._experts = topk_idx.reshape(-1).to(torch.int32)
+        self._tokens = tokens
+        dg.ep_count_dev(ctx, self._experts, pairs, self.num_experts, self._local_rank, self._block_hist, self._counts)
+        if self.distributed:
+            dist.all_gather_into_tensor(self._all_counts, self._counts, group=self.group)
+        dg.ep_layout_dev(ctx, self._all_counts, self.world, self.rank, self.num_experts, self.alignment, self.capacity, self._pair_base,
+                         self.group_ends, self.totals)
+        dg.ep_dispatch_dev(ctx, self._experts, self._local_rank, self._block_hist, self._pair_base, pairs, topk, self.num_experts, self.world,
+                           xq, self.hidden, xsf, dg.sf_aligned_rows(tokens), self.sf_cols, self._peer_data, self._peer_sf, self.sf_stride,
+                           self.capacity, self.pos_of_pair)
+        self._fence()
+        return self.operand(), self.group_ends
+
+    def combine(self, weights: torch.Tensor) -> torch.Tensor:
+        """`result` rows of all ranks (the last grouped GEMM wrote them) -> per-token weighted sums on the token ranks."""
+        self._fence()
+        out = torch.empty((self._tokens, self.out_n), dtype=torch.bfloat16, device=self.device)
+        self.dg.ep_combine_dev(self.ctx, self._experts, self.pos_of_pair, weights, self._tokens, self.topk, self.num_experts, self.world,
+                               self._peer_rows, self.out_n, self.out_n, out, self.out_n)
+        return out
+
+    def overflowed(self) -> bool:
+        """Host read: did the last dispatch need more arena rows than `capacity` on some rank?"""
+        return bool(self.totals[2].item())
+
+    def close(self):
+        if self._base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self._fence()
+        torch.cuda.synchronize(self.device)
+        for p in self._opened:
+            self.dg.peer_close(self.ctx, p)
+        self._opened = []
+        if self.distributed:
+            dist.barrier(group=self.group)
+        self.arena = self.arena_sf = self.result = None
+        self.dg.peer_free(self.ctx, self._base)
+        self._base = None

@@ -159,9 +159,11 @@ int dg_cast_bf16_to_fp8_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, ui
 /* moe.rs:273-296 with layout.rs:218-233 (deepgemm_silu_mul_bf16), fused with the activation quantiser the
  * second grouped GEMM needs: gate_up is (rows, 2n) bf16 with gate = [:, :n] and up = [:, n:]; the value
  * quantised is bf16(silu(gate) * up), silu(g) = g / (1 + exp(-g)); output as dg_cast_bf16_to_fp8_sf gives
- * for that bf16 matrix ((rows, n) e4m3 and packed UE8M0 words), without writing it. */
+ * for that bf16 matrix ((rows, n) e4m3 and packed UE8M0 words), without writing it.  live_rows (may be
+ * NULL): a device word; rows from its value (rounded up to 8) on are left untouched, for an arena whose
+ * row count only the device knows. */
 int dg_silu_mul_cast_fp8_sf(dg_ctx* ctx, const uint16_t* gate_up, uint32_t src_ld, uint32_t rows, uint32_t n, uint32_t gran_k,
-                            uint32_t num_groups, uint8_t* dst, uint32_t* sf);
+                            uint32_t num_groups, uint8_t* dst, uint32_t* sf, const uint32_t* live_rows);
 
 /* ops_sm100.rs:1135 (cast_bf16_to_fp4_packed_sf_dev): dst rows*k/2 bytes. */
 int dg_cast_bf16_to_fp4_packed_sf(dg_ctx* ctx, const uint16_t* src, uint32_t src_ld, uint32_t rows, uint32_t k, uint32_t num_groups,
@@ -199,6 +201,52 @@ int dg_moe_unpack_rows(dg_ctx* ctx, const uint8_t* in, size_t in_pitch, uint32_t
  * multiply-add each; pos < 0 skips a term.  rows / out are bf16 with pitches in elements. */
 int dg_moe_combine(dg_ctx* ctx, const uint16_t* rows, size_t pitch, const int32_t* pos, const float* weights, uint32_t tokens, uint32_t topk,
                    uint32_t n, uint16_t* out, size_t out_pitch);
+
+/* ---- Expert-parallel exchange over peer memory (multi-GPU form of moe.rs:120-252 and :314-360; the
+ * reference is single-GPU).  Rank r owns experts [r * E / W, (r + 1) * E / W).  Each rank exposes its
+ * arena, the arena's packed scale words and its result rows to the other ranks' GPUs; rows are
+ * written to (dispatch) and read from (combine) the owner's memory directly.  Nothing here waits on
+ * another rank: the caller orders the ranks with a collective on the same stream between dispatch and
+ * the grouped GEMM, and between the last GEMM and combine. ---- */
+#define DG_PEER_HANDLE_BYTES 64
+/* Device buffer other processes can map: *ptr is this process's address, handle64 what to send them
+ * (NULL: no handle is made, the buffer stays private to this process). */
+int dg_peer_alloc(dg_ctx* ctx, size_t bytes, void** ptr, unsigned char* handle64);
+/* Map another process's buffer from its handle (same node); *ptr is valid on ctx's device. */
+int dg_peer_open(dg_ctx* ctx, const unsigned char* handle64, void** ptr);
+int dg_peer_close(dg_ctx* ctx, void* ptr);   /* unmap what dg_peer_open returned */
+int dg_peer_free(dg_ctx* ctx, void* ptr);    /* free what dg_peer_alloc returned */
+
+/* Words of the block_hist scratch of dg_ep_count: ceil(pairs / 256) * num_experts. */
+size_t dg_ep_block_hist_words(uint32_t pairs, uint32_t num_experts);
+/* moe.rs:120-173 (expert counts, offsets, destination positions), this rank's part.
+ * expert_of_pair (pairs = tokens * topk, int32, token-major): local_rank[p] = position of pair p among the pairs
+ * of its 256-pair chunk with the same expert (-1 for an expert id outside [0, num_experts): the pair is dropped);
+ * block_hist becomes, per chunk and expert, the number of such pairs in earlier chunks; counts[e] = this rank's
+ * pairs for expert e.  Pairs of one expert keep their order (stable). */
+int dg_ep_count(dg_ctx* ctx, const int32_t* expert_of_pair, uint32_t pairs, uint32_t num_experts, int32_t* local_rank, uint32_t* block_hist,
+                uint32_t* counts);
+/* all_counts (world, num_experts): every rank's counts (all-gathered by the caller).  Groups sit on their owner in
+ * expert order, each starting at a multiple of `alignment`, rows ordered by (source rank, pair index).
+ * pair_base[e] = arena row of this rank's first pair for expert e; group_ends[l] (num_experts / world words) = one
+ * past the last valid row of local expert l, the table dg_m_grouped_fp8_fp4_gemm_contiguous_ends takes;
+ * totals[0..3] = arena rows in use here, valid rows here, 1 if some rank's arena needs more than `capacity` rows
+ * (dispatch then drops the rows that do not fit, and combine skips them), the largest arena in use. */
+int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32_t rank, uint32_t num_experts, uint32_t alignment,
+                 uint32_t capacity, uint32_t* pair_base, uint32_t* group_ends, uint32_t* totals);
+/* moe.rs:176-206 (gather of token rows and scale rows into the grouped layout), across ranks: pair p's e4m3 row
+ * (k bytes) and its sf_cols scale words go to row pos_of_pair[p] of the arena of the rank that owns its expert.
+ * peer_data / peer_sf: device arrays of `world` pointers (every rank's arena (capacity, k) and its scale words
+ * sf[c * peer_sf_stride + row]), entry `rank` being the local buffers.  Padding rows are not written. */
+int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* local_rank, const uint32_t* block_base, const uint32_t* pair_base,
+                   uint32_t pairs, uint32_t topk, uint32_t num_experts, uint32_t world, const uint8_t* data, uint32_t k, const uint32_t* sf,
+                   uint32_t sf_stride, uint32_t sf_cols, void* const* peer_data, void* const* peer_sf, uint32_t peer_sf_stride,
+                   uint32_t capacity, int32_t* pos_of_pair);
+/* moe.rs:314-360 (weighted scatter-accumulate and f32 -> bf16), across ranks and as a gather: out[t, :] =
+ * bf16(sum_j weights[t, j] * rows_j[pos_of_pair[t, j], :]) with rows_j the result buffer (bf16, `pitch` elements per
+ * row) of the rank owning expert_of_pair[t, j]; same arithmetic as dg_moe_combine. */
+int dg_ep_combine(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* pos_of_pair, const float* weights, uint32_t tokens, uint32_t topk,
+                  uint32_t num_experts, uint32_t world, const void* const* peer_rows, size_t pitch, uint32_t n, uint16_t* out, size_t out_pitch);
 
 /* No counterpart in the reference (its device waits spin without bound, deepgemm/src/cuda/common.rs:74-85).
  * Self-test of the bounded wait all kernels here use: launches one warp that waits, for at most limit_us, on a

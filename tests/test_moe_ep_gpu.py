@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import deepgemm_rust_b200 as dg
-from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel
+from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel
 from oracle import oracle as O
 from tests.helpers import dev, fp8_operand_1d, fp8_operand_2d, to_f32
 
@@ -128,3 +128,86 @@ def test_expert_parallel_step_single_rank(ctx):
         seen[e] += 1
     want = O.moe_combine(y_bits, pos, topw.numpy())
     assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want)
+
+
+def arena_layout(expert_of_pair, experts, alignment=128):
+    """numpy restatement of the single-rank arena: groups in expert order, each starting at a multiple of the
+    alignment, pairs of one expert in pair order.  Returns (row of each pair, group ends, rows in use)."""
+    flat = np.asarray(expert_of_pair)
+    ok = (flat >= 0) & (flat < experts)
+    counts = np.bincount(flat[ok], minlength=experts)
+    padded = (counts + alignment - 1) // alignment * alignment
+    starts = np.cumsum(padded) - padded
+    pos = np.full(flat.size, -1, np.int64)
+    seen = np.zeros(experts, np.int64)
+    for p, e in enumerate(flat):
+        if ok[p]:
+            pos[p] = starts[e] + seen[e]
+            seen[e] += 1
+    return pos, starts + counts, int(padded.sum())
+
+
+def test_peer_exchange_single_rank(ctx):
+    experts, topk, tokens, hidden, n = 8, 3, 700, 512, 256          # 2100 pairs: nine ranking chunks, the last one ragged
+    g = torch.Generator().manual_seed(21)
+    topw, topi = torch.softmax(torch.randn((tokens, experts), generator=g), -1).topk(topk, dim=-1)
+    topi[topi == 5] = 6                                               # an expert nobody routes to
+    topi[3, 1] = -1                                                   # a dropped pair
+    topi[10, 0] = experts                                             # an id out of range is dropped as well
+    _, xq, xsf = fp8_operand_1d(tokens, hidden, 31)
+    _, wq, wsf, _ = fp8_operand_2d(experts * n, hidden, 32, experts)
+    pe = PeerExpertParallel(ctx, experts, topk, tokens, hidden, n)
+    try:
+        for step in range(2):                                         # the second step reuses every buffer
+            a_op, ends = pe.dispatch(topi.cuda(), dev(xq), dev(xsf))
+            ctx.sync()
+            pos, want_ends, rows_in_use = arena_layout(topi.reshape(-1).numpy(), experts)
+            assert np.array_equal(pe.pos_of_pair.cpu().numpy()[:pos.size], pos)
+            assert np.array_equal(ends.cpu().numpy().view(np.uint32), want_ends)
+            totals = pe.totals.cpu().numpy()
+            assert totals[0] == rows_in_use and totals[1] == (pos >= 0).sum() and totals[2] == 0 and totals[3] == rows_in_use
+            arena = pe.arena.cpu().numpy()
+            sf = pe.arena_sf.cpu().numpy().view(np.uint32).reshape(pe.sf_cols, pe.sf_stride)
+            xsf2 = xsf.reshape(pe.sf_cols, -1)
+            live = np.nonzero(pos >= 0)[0]
+            assert np.array_equal(arena[pos[live]], xq[live // topk])
+            assert np.array_equal(sf[:, pos[live]], xsf2[:, live // topk])
+            untouched = np.ones(pe.capacity, bool)
+            untouched[pos[live]] = False
+            assert not arena[untouched].any() and not sf[:, untouched].any()
+            # the grouped GEMM takes the group-end table as it is and writes the buffer the combine reads
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, dg.LpOperand(dev(wq), dev(wsf), experts * n, hidden, hidden),
+                                                          dg.Sm100Out.Bf16(pe.result, n), experts)
+            out = pe.combine(topw.cuda().contiguous())
+            ctx.sync()
+            y_bits = pe.result.view(torch.int16).cpu().numpy().view(np.uint16)
+            flat = topi.reshape(-1).numpy()
+            for e in range(experts):
+                rows = pos[(flat == e)].astype(np.uint32)
+                if rows.size:
+                    want = O.lp_gemm_rows(arena, pe.arena_sf.cpu().numpy().view(np.uint32), 8, 128, 1, pe.capacity, rows, wq, wsf, 8, 128,
+                                          experts, n, np.arange(e * n, (e + 1) * n, dtype=np.uint32), hidden)
+                    assert O.calc_diff(to_f32(pe.result)[rows.astype(np.int64)], want) <= 2e-5
+            want = O.moe_combine(y_bits, pos.reshape(tokens, topk).astype(np.int32), topw.numpy())
+            assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want)
+            assert not pe.overflowed()
+    finally:
+        pe.close()
+
+
+def test_peer_exchange_reports_overflow(ctx):
+    # an arena too small for the routing: rows that do not fit are dropped, flagged, and skipped by the combine
+    experts, topk, tokens, hidden, n = 4, 2, 256, 512, 128
+    topi = torch.zeros((tokens, topk), dtype=torch.int64)
+    topi[:, 1] = 1
+    _, xq, xsf = fp8_operand_1d(tokens, hidden, 41)
+    pe = PeerExpertParallel(ctx, experts, topk, tokens, hidden, n, capacity=384)
+    try:
+        pe.dispatch(topi.cuda(), dev(xq), dev(xsf))
+        ctx.sync()
+        assert pe.overflowed()
+        pos = pe.pos_of_pair.cpu().numpy().reshape(tokens, topk)
+        assert np.array_equal(pos[:, 0], np.arange(tokens))           # expert 0 fits in rows [0, 256)
+        assert np.array_equal(pos[:128, 1], 256 + np.arange(128)) and np.all(pos[128:, 1] == -1)
+    finally:
+        pe.close()

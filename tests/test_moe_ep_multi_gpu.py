@@ -1,4 +1,4 @@
-"""Expert-parallel dispatch -> grouped GEMM -> combine on 2 GPUs over NCCL, checked on every rank against
+"""Expert-parallel dispatch -> grouped GEMM -> combine on 2 GPUs, over NCCL all-to-all and over peer memory, checked on every rank against
 a local recomputation: each rank also holds all experts' weights (same seed), so for its own tokens
 out[t] = sum_j w[t,j] * (x_t . W[e_j]^T) can be computed with the dense GEMM path one expert at a time.
 Skipped when fewer than two GPUs are visible."""
@@ -20,7 +20,7 @@ def _rank_main(rank, world, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import deepgemm_rust_b200 as dg
-        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel
+        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel
         from oracle import oracle as O
         dev = torch.device("cuda", rank)
         ctx = dg.DgContext(rank)
@@ -54,7 +54,20 @@ def _rank_main(rank, world, port, results):
         pos = (topi * tokens + torch.arange(tokens, device=dev).unsqueeze(1)).to(torch.int32).cpu().numpy()
         want = O.moe_combine(y_all.view(torch.int16).cpu().numpy().view(np.uint16), pos, topw.cpu().numpy())
         got = out.view(torch.int16).cpu().numpy().view(np.uint16)
-        results[rank] = bool(np.array_equal(got, want))
+        ok = bool(np.array_equal(got, want))
+        # the same step over peer memory: rows written into / read from the owner's buffers directly
+        pe = PeerExpertParallel(ctx, experts, topk, tokens, k, n)
+        for _ in range(2):
+            a_op, ends = pe.dispatch(topi, xq, xsf)
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, dg.LpOperand(wq_local, wsf_local, local * n, k, k),
+                                                          dg.Sm100Out.Bf16(pe.result, n), local)
+            out2 = pe.combine(topw)
+            ctx.sync()
+            ok = ok and bool(np.array_equal(out2.view(torch.int16).cpu().numpy().view(np.uint16), want)) and not pe.overflowed()
+            totals = pe.totals.cpu().numpy()
+            ok = ok and int(totals[1]) == plan.n_recv and int(totals[0]) == plan.m_pad
+        pe.close()
+        results[rank] = ok
         ctx.close()
     finally:
         dist.destroy_process_group()
