@@ -16,6 +16,9 @@ Workloads (all synthetic: seeded N(0,1) bf16 matrices quantised to e4m3 with per
               GEMM (N=4096, K=7168) + silu(gate)*up quantised to e4m3 + down grouped GEMM (N=7168, K=2048)
               on that activation + all-to-all combine and weighted reduction.  Flops count the routed
               (unpadded) rows of both GEMMs only.
+  configs     (report, one GPU) every benchmark configuration launched alone against its roofline: the ten dense
+              shapes, MXFP4 and FP8xFP4 4096x7168x7168, the quantisers, the masked decode GEMM with FP8 output, and the
+              grouped GEMM pair with its row movers for one rank of a 1-GPU and of an 8-GPU job.
 The metric is whole-job TFLOP/s: 2*M*N*K summed over the GEMMs of a step, times ranks, over the
 step time (CUDA events, max over ranks).  `e2e` is the same pass driven from pinned host buffers
 (operands copied host->device and the result device->host inside the timed region).
@@ -206,10 +209,6 @@ class DenseWork:
                 e1.record()
                 record.append((e0, e1))
 
-    def routed_rows(self):
-        """Valid arena rows of this rank in the last step (a host read, outside any timed region)."""
-        return int(self.peer.totals[1].item()) if self.peer is not None else self.rows
-
     def e2e_setup(self):
         torch = self.torch
         self.host = []
@@ -393,13 +392,124 @@ class MoeWork:
         return statistics.median(times[1:]), plan.n_recv
 
 
+
+def run_config_table(args, torch, dg, ctx, dev, peaks):
+    """`--workload configs`: every benchmark configuration on one GPU, each launch alone behind an L2 flush, against the
+    bound its algorithmic bytes and flops give (slower of tensor peak and HBM).  A report, not the bench line: prints one
+    JSON object {"rows": [...]}.  Tensor peaks: 2 x (FP8) or 4 x (FP4) the measured bf16 figure (burst: launches timed alone)."""
+    hbm, tc8, tc4 = peaks["hbm_gbs"] * 1e9, 2e12 * peaks["bf16_tflops"], 4e12 * peaks["bf16_tflops"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    rows = []
+
+    def timeit(fn, reps=6):
+        times = []
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e-3)
+        return statistics.median(times[1:])
+
+    def add(name, t, flops, nbytes, tc):
+        t_tc, t_hbm = (flops / tc if flops else 0.0), nbytes / hbm
+        bound = "tensor" if t_tc >= t_hbm else "hbm"
+        row = {"config": name, "us": round(t * 1e6, 1), "bound": bound, "roofline_us": round(max(t_tc, t_hbm) * 1e6, 1),
+               "frac": round(max(t_tc, t_hbm) / t, 3), "gbs": round(nbytes / t / 1e9, 1)}
+        if flops:
+            row["tflops"] = round(flops / t / 1e12, 1)
+        rows.append(row)
+        print(json.dumps(row), file=sys.stderr, flush=True)
+
+    def randn(r, c):
+        return torch.randn((r, c), generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+
+    def sf_bytes(k, gran, r):
+        return 4 * ((k + 4 * gran - 1) // (4 * gran)) * r
+
+    # config 2: dense FP8
+    for (m, n, k) in DENSE_SHAPES:
+        aq, asf = dg.cast_bf16_to_fp8_sf_dev(ctx, randn(m, k), k, m, k, 128)
+        bq, bsf = dg.cast_bf16_to_fp8_sf_dev(ctx, randn(n, k), k, n, k, 128)
+        d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        a, b, out = dg.LpOperand(aq, asf, m, k, k), dg.LpOperand(bq, bsf, n, k, k), dg.Sm100Out.Bf16(d, n)
+        t = timeit(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, out))
+        add(f"dense fp8 {m}x{n}x{k}", t, 2.0 * m * n * k, m * k + n * k + 2 * m * n + sf_bytes(k, 128, m + n), tc8)
+    # config 3: MXFP4 and FP8 x FP4
+    m, n, k = 4096, 7168, 7168
+    x, w = randn(m, k), randn(n, k)
+    a4q, a4sf = dg.cast_bf16_to_fp4_packed_sf_dev(ctx, x, k, m, k, 1, dg.SF_RULE_RANGE_FIT)
+    b4q, b4sf = dg.cast_bf16_to_fp4_packed_sf_dev(ctx, w, k, n, k, 1, dg.SF_RULE_RANGE_FIT)
+    a8q, a8sf = dg.cast_bf16_to_fp8_sf_dev(ctx, x, k, m, k, 32)
+    d = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    out = dg.Sm100Out.Bf16(d, n)
+    a4, b4 = dg.LpOperand(a4q, a4sf, m, k, k, 4, 32), dg.LpOperand(b4q, b4sf, n, k, k, 4, 32)
+    a8 = dg.LpOperand(a8q, a8sf, m, k, k, 8, 32)
+    t = timeit(lambda: dg.fp8_fp4_gemm_dev(ctx, a4, b4, out))
+    add(f"mxfp4 {m}x{n}x{k}", t, 2.0 * m * n * k, (m + n) * k // 2 + 2 * m * n + sf_bytes(k, 32, m + n), tc4)
+    t = timeit(lambda: dg.fp8_fp4_gemm_dev(ctx, a8, b4, out))
+    add(f"fp8 x fp4 {m}x{n}x{k}", t, 2.0 * m * n * k, m * k + n * k // 2 + 2 * m * n + sf_bytes(k, 32, m + n), tc8)
+    del x, w, a4q, b4q, a8q, d
+    # quantisers
+    for (r, c) in [(4096, 7168), (7168, 16384)]:
+        src = randn(r, c)
+        t = timeit(lambda: dg.cast_bf16_to_fp8_sf_dev(ctx, src, c, r, c, 128))
+        add(f"quantise bf16->e4m3 {r}x{c} gran 128", t, 0.0, 3 * r * c + sf_bytes(c, 128, r), tc8)
+        t = timeit(lambda: dg.cast_bf16_to_fp4_packed_sf_dev(ctx, src, c, r, c, 1, dg.SF_RULE_RANGE_FIT))
+        add(f"quantise bf16->e2m1 {r}x{c}", t, 0.0, 2.5 * r * c + sf_bytes(c, 32, r), tc8)
+    del src
+    # config 5: masked decode GEMM, FP8 output
+    g, m_max, n, k = 32, 256, 4096, 7168
+    masked = torch.randint(0, m_max + 1, (g,), generator=torch.Generator().manual_seed(4000), dtype=torch.int32)
+    valid = int(masked.sum())
+    aq, asf = dg.cast_bf16_to_fp8_sf_dev(ctx, randn(g * m_max, k), k, g * m_max, k, 128, g)
+    bq, bsf = dg.cast_bf16_to_fp8_sf_dev(ctx, randn(g * n, k), k, g * n, k, 128, g)
+    d8 = torch.empty((g * m_max, n), dtype=torch.uint8, device=dev)
+    sfd = torch.zeros(g * (n // 128) * m_max, dtype=torch.int32, device=dev)
+    a, b, mm = dg.LpOperand(aq, asf, m_max, k, k), dg.LpOperand(bq, bsf, g * n, k, k), masked.to(dev)
+    t = timeit(lambda: dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, a, mm, b, dg.Sm100Out.Fp8(d8, n, sfd), g, valid // g))
+    add(f"masked fp8-out {g} experts x <= {m_max} rows ({valid} valid), N={n} K={k}", t, 2.0 * valid * n * k,
+        valid * k + g * n * k + valid * n * (1 + 1 / 32) + sf_bytes(k, 128, valid + g * n), tc8)
+    del aq, bq, d8
+    # config 4: the two contiguous grouped GEMMs and the row movers around them, one rank of a 1-GPU and of an 8-GPU job
+    for experts in (MOE["experts"], MOE["experts"] // 8):
+        saved = dict(MOE)
+        MOE["experts"] = experts
+        moe = MoeWork(torch, None, dg, ctx, dev, 0, 1, "peer")
+        MOE.update(saved)
+        pe, c = moe.peer, moe.c
+        a_op, ends = pe.dispatch(moe.topi, moe.xq, moe.xsf)
+        rows_valid = moe.routed_rows()
+        h_out, y_out = dg.Sm100Out.Bf16(moe.h, c["gate_up_n"]), dg.Sm100Out.Bf16(pe.result, c["down_n"])
+        act_op = dg.LpOperand(moe.act[0], moe.act[1], pe.capacity, c["down_k"], c["down_k"])
+        tag = f"{experts} local experts, {rows_valid} rows"
+        t = timeit(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, moe.w1, h_out, experts))
+        n, k = c["gate_up_n"], c["hidden"]
+        add(f"grouped gate/up ({tag})", t, 2.0 * rows_valid * n * k, rows_valid * k + experts * n * k + 2 * rows_valid * n + sf_bytes(k, 128, rows_valid + experts * n), tc8)
+        t = timeit(lambda: dg.silu_mul_cast_fp8_sf_dev(ctx, moe.h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=moe.act))
+        add(f"silu*up + quantise ({tag})", t, 0.0, rows_valid * c["down_k"] * 5, tc8)
+        n, k = c["down_n"], c["down_k"]
+        t = timeit(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, act_op, ends, moe.w2, y_out, experts))
+        add(f"grouped down ({tag})", t, 2.0 * rows_valid * n * k, rows_valid * k + experts * n * k + 2 * rows_valid * n + sf_bytes(k, 128, rows_valid + experts * n), tc8)
+        t = timeit(lambda: pe.dispatch(moe.topi, moe.xq, moe.xsf))
+        add(f"route + dispatch, local ({tag})", t, 0.0, moe.tokens * c["hidden"] + rows_valid * c["hidden"], tc8)
+        t = timeit(lambda: pe.combine(moe.topw))
+        add(f"combine, local ({tag})", t, 0.0, 2 * rows_valid * c["down_n"] + 2 * moe.tokens * c["down_n"], tc8)
+        pe.close()
+        del moe, pe, a_op, act_op, h_out, y_out
+        torch.cuda.empty_cache()
+    print(json.dumps({"rows": rows, "peaks": peaks, "note": "each launch alone, L2 flushed before it; frac = roofline time / measured time"}))
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="dgb200")
-    ap.add_argument("--workload", default="dsv3", choices=["dsv3", "dense_fp8", "moe_ep"])
+    ap.add_argument("--workload", default="dsv3", choices=["dsv3", "dense_fp8", "moe_ep", "configs"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--moe-experts", type=int, default=None, help="moe_ep: total experts (default 256); 32 gives one rank of an 8-GPU job")
@@ -432,6 +542,12 @@ def main():
     dev = torch.device("cuda", local_rank)
     ctx = dg.DgContext(local_rank)
     peaks = measured_peaks()
+
+    if args.workload == "configs":
+        if world > 1:
+            raise SystemExit("--workload configs is a single-GPU report")
+        run_config_table(args, torch, dg, ctx, dev, peaks)
+        return
 
     # ---- build the workload (untimed): operands resident in HBM, quantised by the library's own kernels
     dense = DenseWork(torch, dg, ctx, dev, 1000 + rank) if args.workload in ("dsv3", "dense_fp8") else None
