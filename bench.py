@@ -452,6 +452,8 @@ def run_config_table(args, torch, dg, ctx, dev, peaks):
     add(f"mxfp4 {m}x{n}x{k}", t, 2.0 * m * n * k, (m + n) * k // 2 + 2 * m * n + sf_bytes(k, 32, m + n), tc4)
     t = timeit(lambda: dg.fp8_fp4_gemm_dev(ctx, a8, b4, out))
     add(f"fp8 x fp4 {m}x{n}x{k}", t, 2.0 * m * n * k, m * k + n * k // 2 + 2 * m * n + sf_bytes(k, 32, m + n), tc8)
+    t = timeit(lambda: dg.bf16_gemm_dev(ctx, x, k, m, w, k, n, k, out))
+    add(f"bf16 {m}x{n}x{k}", t, 2.0 * m * n * k, 2 * (m + n) * k + 2 * m * n, 1e12 * peaks["bf16_tflops"])
     del x, w, a4q, b4q, a8q, d
     # quantisers
     for (r, c) in [(4096, 7168), (7168, 16384)]:

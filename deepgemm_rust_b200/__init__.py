@@ -89,6 +89,7 @@ _gemm_contig_ends = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_ends", C.c_int,
                            C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
 _gemm_contig_static = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_static", C.c_int, C.c_int, _vp, C.POINTER(_LpOperand), _vp,
                              C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_bf16_gemm = _proto("dg_bf16_gemm", C.c_int, _vp, _vp, _u32, _u32, _vp, _u32, _u32, _u32, C.POINTER(_Out), C.POINTER(_Epilogue))
 _gemm_masked = _proto("dg_m_grouped_fp8_fp4_gemm_masked", C.c_int, _vp, C.POINTER(_LpOperand), _vp, C.POINTER(_LpOperand),
                       C.POINTER(_Out), _u32, _u32, C.POINTER(_Epilogue))
 _bmm = _proto("dg_fp8_fp4_bmm", C.c_int, _vp, C.POINTER(_LpOperand), C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
@@ -256,6 +257,30 @@ def fp8_fp4_gemm_dev(ctx: DgContext, a: LpOperand, b: LpOperand, out: Sm100Out, 
     """ops_sm100.rs:719"""
     ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
     _check(_gemm(ctx._h, C.byref(ca), C.byref(cb), C.byref(co), C.byref(ce)))
+
+
+def bf16_gemm_dev(ctx, a: torch.Tensor, a_ld: int, m: int, b: torch.Tensor, b_ld: int, n: int, k: int, out, epi=None):
+    """ops_sm100.rs:893: D[m,n] = A[m,k] . B[n,k]^T, bf16 K-major operands, f32 accumulation."""
+    co, ce = out._c(), _epi(epi)
+    _check(_bf16_gemm(ctx._h, _vp(a.data_ptr()), a_ld, m, _vp(b.data_ptr()), b_ld, n, k, C.byref(co), C.byref(ce)))
+
+
+@dataclass
+class Bf16Tensor:
+    """deepgemm/src/types.rs (Bf16Tensor): a K-major bf16 matrix view."""
+    data: torch.Tensor
+    rows: int
+    k: int
+    ld: Optional[int] = None
+
+    def __post_init__(self):
+        if self.ld is None:
+            self.ld = self.k
+
+
+def bf16_gemm_nt_dev(ctx, a: "Bf16Tensor", b: "Bf16Tensor", out: torch.Tensor, out_ld: int):
+    """deepgemm/src/ops.rs:769: bf16 output (m, out_ld)."""
+    bf16_gemm_dev(ctx, a.data, a.ld, a.rows, b.data, b.ld, b.rows, a.k, Sm100Out.Bf16(out, out_ld))
 
 
 def m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, m_indices: torch.Tensor, b, out, num_groups: int, epi=None):

@@ -341,11 +341,12 @@ struct Problem {
     uint32_t n, k, groups;
     uint32_t expected_m;
     const uint32_t* layout;
+    bool bf16 = false;     // operands are bf16 rows described as 2k bytes each; no scale factors (dg_bf16_gemm)
 };
 
-template <bool kMXF4, uint32_t kOut, uint32_t kCtas>
+template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
 cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
-    auto kernel = dg::dg_gemm_kernel<kMXF4, kOut, kCtas>;
+    auto kernel = dg::dg_gemm_kernel<kFmt, kOut, kCtas>;
     // the opt-in is per device; remember which devices already have it
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -371,11 +372,12 @@ cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem,
     return cudaLaunchKernelEx(&cfg, kernel, p, maps[0], maps[1], maps[2], maps[3], maps[4]);
 }
 
-template <bool kMXF4, uint32_t kCtas>
+template <uint32_t kFmt, uint32_t kCtas>
 cudaError_t launch_by_out(int kind, const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
-    if (kind == DG_OUT_BF16) return launch_kernel<kMXF4, dg::kOutBf16, kCtas>(p, grid, smem, stream, maps);
-    if (kind == DG_OUT_F32) return launch_kernel<kMXF4, dg::kOutF32, kCtas>(p, grid, smem, stream, maps);
-    return launch_kernel<kMXF4, dg::kOutFp8, kCtas>(p, grid, smem, stream, maps);
+    if (kind == DG_OUT_BF16) return launch_kernel<kFmt, dg::kOutBf16, kCtas>(p, grid, smem, stream, maps);
+    if (kind == DG_OUT_F32) return launch_kernel<kFmt, dg::kOutF32, kCtas>(p, grid, smem, stream, maps);
+    if constexpr (kFmt != dg::kFmtBf16) return launch_kernel<kFmt, dg::kOutFp8, kCtas>(p, grid, smem, stream, maps);
+    return cudaErrorInvalidValue;
 }
 
 int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi, const Problem& pr) {
@@ -391,9 +393,9 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     const bool contiguous = pr.type == DG_GEMM_M_GROUPED_CONTIGUOUS;
     const uint32_t a_groups = contiguous || pr.type == DG_GEMM_NORMAL ? 1 : pr.groups;
     const uint32_t b_groups = pr.type == DG_GEMM_NORMAL ? 1 : pr.groups;
-    int rc = check_operand(a, "a", pr.m * a_groups, a_groups);
+    int rc = pr.bf16 ? DG_OK : check_operand(a, "a", pr.m * a_groups, a_groups);
     if (rc) return rc;
-    rc = check_operand(b, "b", pr.n * b_groups, b_groups);
+    rc = pr.bf16 ? DG_OK : check_operand(b, "b", pr.n * b_groups, b_groups);
     if (rc) return rc;
     const uint32_t d_rows = pr.m * a_groups;
     const uint32_t d_elem = out->kind == DG_OUT_F32 ? 4 : (out->kind == DG_OUT_FP8 ? 1 : 2);
@@ -459,15 +461,16 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     }
     const uint32_t sfa_cols = dg_sf_packed_cols(pr.k, a->gran_k), sfb_cols = dg_sf_packed_cols(pr.k, b->gran_k);
     {
+        // bf16 operands carry no scales: the kernel never issues these loads, the maps only have to be well-formed
         uint64_t dims[2] = {align4(pr.m), static_cast<uint64_t>(sfa_cols) * a_groups};
         uint64_t strides[1] = {static_cast<uint64_t>(align4(pr.m)) * 4};
         uint32_t box[2] = {128, sfa_words};
-        rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, a->sf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA");
+        rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? a->data : a->sf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA");
         if (rc) return rc;
         uint64_t bdims[2] = {align4(pr.n), static_cast<uint64_t>(sfb_cols) * b_groups};
         uint64_t bstrides[1] = {static_cast<uint64_t>(align4(pr.n)) * 4};
         uint32_t bbox[2] = {sf_block_n, sfb_words};
-        rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, b->sf, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB");
+        rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? b->data : b->sf, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB");
         if (rc) return rc;
     }
     {
@@ -538,10 +541,12 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     const int kernel_out = splits > 1 ? DG_OUT_F32 : out->kind;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     cudaError_t ce;
-    if (mxf4) ce = ctas == 2 ? launch_by_out<true, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
-                             : launch_by_out<true, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
-    else ce = ctas == 2 ? launch_by_out<false, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
-                        : launch_by_out<false, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
+    if (pr.bf16) ce = ctas == 2 ? launch_by_out<dg::kFmtBf16, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
+                                : launch_by_out<dg::kFmtBf16, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
+    else if (mxf4) ce = ctas == 2 ? launch_by_out<dg::kFmtMxf4, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
+                                  : launch_by_out<dg::kFmtMxf4, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
+    else ce = ctas == 2 ? launch_by_out<dg::kFmtMxf8f6f4, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
+                        : launch_by_out<dg::kFmtMxf8f6f4, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
     if (ce == cudaSuccess && splits > 1) {
         const uint64_t threads = static_cast<uint64_t>(pr.m) * ceil_div(pr.n, 4);
         const uint32_t blocks = static_cast<uint32_t>((threads + 255) / 256);
@@ -582,6 +587,19 @@ int dg_fp8_fp4_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b,
     if (out->kind == DG_OUT_FP8) return fail(DG_ERR_SHAPE, "the dynamic FP8 output is only supported by the batched and masked APIs");
     Problem pr = {DG_GEMM_NORMAL, a->rows, b->rows, a->k, 1, a->rows, nullptr};
     return launch_gemm(ctx, a, b, out, epi, pr);
+}
+
+int dg_bf16_gemm(dg_ctx* ctx, const uint16_t* a, uint32_t a_ld, uint32_t m, const uint16_t* b, uint32_t b_ld, uint32_t n, uint32_t k,
+                 const dg_out* out, const dg_epilogue* epi) {
+    if (!ctx || !a || !b || !out) return fail(DG_ERR_SHAPE, "null argument");
+    if (out->kind == DG_OUT_FP8) return fail(DG_ERR_UNSUPPORTED, "the bf16 GEMM writes bf16 or f32 outputs");
+    if (k == 0 || k % 8 != 0) return fail(DG_ERR_SHAPE, "bf16 k (%u) must be a positive multiple of 8", k);
+    if (a_ld < k || b_ld < k || a_ld % 8 != 0 || b_ld % 8 != 0) return fail(DG_ERR_SHAPE, "leading dimensions must be >= k and multiples of 8 elements");
+    // the kernel sees K-major rows of 2k bytes: same tiles, same TMA boxes, same 32-byte UMMA steps as the 8-bit formats
+    dg_lp_operand a8 = {a, nullptr, m, 2 * k, 2 * a_ld, 8, 128, 0, static_cast<size_t>(m) * 2 * a_ld, 0};
+    dg_lp_operand b8 = {b, nullptr, n, 2 * k, 2 * b_ld, 8, 128, 0, static_cast<size_t>(n) * 2 * b_ld, 0};
+    Problem pr = {DG_GEMM_NORMAL, m, n, 2 * k, 1, m, nullptr, true};
+    return launch_gemm(ctx, &a8, &b8, out, epi, pr);
 }
 
 int dg_m_grouped_fp8_fp4_gemm_contiguous_ends(dg_ctx* ctx, const dg_lp_operand* a, const uint32_t* group_ends, const dg_lp_operand* b,

@@ -29,6 +29,7 @@ namespace dg {
 
 enum GemmType : uint32_t { kGemmNormal = 0, kGemmContiguous = 1, kGemmMasked = 2, kGemmBatched = 3 };
 enum OutKind : uint32_t { kOutBf16 = 0, kOutF32 = 1, kOutFp8 = 2 };
+enum OperandFmt : uint32_t { kFmtMxf8f6f4 = 0, kFmtMxf4 = 1, kFmtBf16 = 2 };
 
 constexpr uint32_t kBlockM = 128;          // UMMA M, rows of A per tile
 constexpr uint32_t kBlockKBytes = 128;     // one 128-byte swizzle row of K per TMA box / UMMA group ("half" of a double stage)
@@ -191,13 +192,16 @@ DG_DEVICE SfPlan sf_plan(uint32_t gran, uint32_t block_k_elems) {
     return s;
 }
 
-template <bool kMXF4, uint32_t kOut, uint32_t kCtas>
+// kFmt: kFmtMxf8f6f4 (e4m3 / expanded e2m1 operands, block-scaled), kFmtMxf4 (packed e2m1, block-scaled) or
+// kFmtBf16 (bf16 operands seen as K-major rows of 2k bytes, kind::f16, no scale factors: bf16_gemm_sm100.rs).
+template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
 __global__ void __launch_bounds__(kNumThreads, 1)
 dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                const __grid_constant__ CUtensorMap tmap_d) {
     // a stage holds one or two 128-byte K slabs per operand (block_k_elems = halves x 128 e4m3 / 256 e2m1):
     // two slabs halve the per-stage bookkeeping (waits, commits) the UMMA warp does per UMMA
+    constexpr bool kMXF4 = kFmt == kFmtMxf4, kScaled = kFmt != kFmtBf16;
     constexpr uint32_t kHalfElems = kMXF4 ? 256 : 128;
     const uint32_t kBlockKElems = p.block_k_elems;
     const uint32_t halves = kBlockKElems / kHalfElems;
@@ -280,7 +284,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             const int32_t row_b = static_cast<int32_t>(t.n0 + cta_rank * load_n);
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
-                bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -322,7 +326,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             Scheduler sched(p, kCtas);
             Tile t;
             uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0;
-            const uint32_t idesc = make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b);
+            const uint32_t idesc = kScaled ? make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b)
+                                           : make_idesc_bf16(kBlockM * kCtas, block_n);
             const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
 #ifdef DG_PROFILE
@@ -338,7 +343,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + e * block_n;
                 for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                    bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                    bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
 #ifdef DG_PROFILE
                     if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -386,9 +391,14 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes + h * b_half), 0, 1024, 2);
                         if (leader_lane) {
                             #pragma unroll
-                            for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k)
-                                umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
-                                                                a_cols[k], b_cols[k], (kb != t.kb0 || h != 0 || k != 0) ? 1u : 0u);
+                            for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+                                const uint32_t accumulate = (kb != t.kb0 || h != 0 || k != 0) ? 1u : 0u;
+                                if constexpr (kScaled)
+                                    umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
+                                                                    a_cols[k], b_cols[k], accumulate);
+                                else
+                                    umma_f16<kCtas>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idesc, accumulate);
+                            }
                         }
                     }
                     if (leader_lane) {
@@ -420,7 +430,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         bool ok = true;
         while (ok && sched.next(t)) {
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                bool need_a = kb % plan_a.period == 0, need_b = kb % plan_b.period == 0;
+                bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif

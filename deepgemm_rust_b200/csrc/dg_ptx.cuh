@@ -211,6 +211,11 @@ DG_DEVICE uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32
 DG_DEVICE uint32_t make_idesc_block_scaled(uint32_t m, uint32_t n, uint32_t a_fmt, uint32_t b_fmt) {
     return (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24);
 }
+// kind::f16 instruction descriptor, bf16 operands, f32 accumulate, both K-major:
+//   [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format, [17,23) N >> 3, [24,29) M >> 4.
+DG_DEVICE uint32_t make_idesc_bf16(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
 DG_DEVICE uint32_t idesc_with_sf_ids(uint32_t idesc, uint32_t a_id, uint32_t b_id) {
     return idesc | (b_id << 4) | (a_id << 29);
 }
@@ -245,6 +250,23 @@ DG_DEVICE void umma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_de
                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
                 : "memory");
     }
+}
+
+// Plain (not block-scaled) 16-bit UMMA: K = 16 elements = 32 bytes per instruction.
+template <int CTAS>
+DG_DEVICE void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (CTAS == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n" ::"r"(d_tmem),
+            "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
 }
 
 // Scale-factor copy shared memory -> TMEM: 32 rows x 16 bytes replicated to the four

@@ -82,6 +82,12 @@ typedef struct {
 /* ops_sm100.rs:719 (fp8_fp4_gemm_dev): D[m,n] = alpha * A[m,k] . B[n,k]^T */
 int dg_fp8_fp4_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi);
 
+/* ops_sm100.rs:893 (bf16_gemm_dev; ops.rs:769 bf16_gemm_nt_dev routes here on Blackwell): D[m,n] = A[m,k] . B[n,k]^T
+ * with bf16 K-major operands (leading dimensions in elements, multiples of 8), f32 accumulation, bf16 or f32
+ * output; alpha and accumulate as for the FP8 GEMM.  Same kernel skeleton with kind::f16 UMMAs and no scale path. */
+int dg_bf16_gemm(dg_ctx* ctx, const uint16_t* a, uint32_t a_ld, uint32_t m, const uint16_t* b, uint32_t b_ld, uint32_t n, uint32_t k,
+                 const dg_out* out, const dg_epilogue* epi);
+
 /* ops_sm100.rs:759 (m_grouped_fp8_fp4_gemm_contiguous_dev).  a: (m_total, k) arena, every group
  * starts at a multiple of the mk alignment; m_indices (device, m_total int32): group of each
  * row, -1 for padding; b.rows = num_groups * n.  The group-end table is built in a scratch

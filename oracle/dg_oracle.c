@@ -577,6 +577,21 @@ DGO_API void dgo_moe_combine(const uint16_t* rows, size_t pitch, const int32_t* 
         }
 }
 
+/* reference.rs:117-129 (ref_bf16_gemm_nt): out[m,n] = sum_k a[m,k] * b[n,k] over bf16 bit patterns, f64
+ * accumulation in k order, rounded to f32 once. */
+DGO_API void dgo_ref_bf16_gemm_nt(const uint16_t* a, uint32_t m, const uint16_t* b, uint32_t n, uint32_t k, float* out, int threads) {
+#ifdef _OPENMP
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1) schedule(static)
+#endif
+    for (int64_t mi = 0; mi < (int64_t)m; ++mi)
+        for (uint32_t ni = 0; ni < n; ++ni) {
+            double acc = 0.0;
+            for (uint32_t ki = 0; ki < k; ++ki)
+                acc += (double)dgo_bf16_to_f32(a[(size_t)mi * k + ki]) * (double)dgo_bf16_to_f32(b[(size_t)ni * k + ki]);
+            out[(size_t)mi * n + ni] = (float)acc;
+        }
+}
+
 /* SiLU-and-mul (cuda/layout.rs:218-233 as called from moe.rs:273-296): out[r,c] = bf16(silu(gate) * up) on a
  * (rows, 2n) gate|up matrix of bf16 bits, silu(g) = g / (1 + exp(-g)).  The reference's device code uses the
  * fast-math exponential, which no host function reproduces bit for bit; exp is therefore written out here

@@ -325,6 +325,20 @@ def moe_combine(rows_bits, pos, w):
     return out
 
 
+_ref_bf16 = _sig("dgo_ref_bf16_gemm_nt", None, _u16p, C.c_uint32, _u16p, C.c_uint32, C.c_uint32, _f32p, C.c_int)
+
+
+def ref_bf16_gemm_nt(a_bits, b_bits, threads=1):
+    """reference.rs:117: (m, k) x (n, k)^T over bf16 bit patterns, f64 accumulation -> f32."""
+    a_bits = np.ascontiguousarray(a_bits, np.uint16)
+    b_bits = np.ascontiguousarray(b_bits, np.uint16)
+    m, k = a_bits.shape
+    n = b_bits.shape[0]
+    out = np.zeros((m, n), np.float32)
+    _ref_bf16(a_bits, m, b_bits, n, k, out, threads)
+    return out
+
+
 _silu_mul = _sig("dgo_silu_mul_bf16", None, _u16p, C.c_uint32, C.c_uint32, C.c_uint32, _u16p)
 
 

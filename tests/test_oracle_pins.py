@@ -277,6 +277,18 @@ def test_sf_transforms():
     assert np.array_equal(w2d, O.transform_sf1d_packed(np.repeat(sf2, 128, axis=0), k, 128))
 
 
+def test_bf16_reference_gemm_on_the_reference_test_pattern():
+    # tests/e2e.rs:188-217 inputs; reference.rs:117-129 accumulates in f64 and rounds once, so it must agree with a
+    # float64 matmul of the same bf16 values to f32 rounding
+    m, n, k = 128, 256, 512
+    a = O.bf16_bits(((np.arange(m * k) % 13).astype(np.float32) / np.float32(13.0) - np.float32(0.5)).reshape(m, k))
+    b = O.bf16_bits(((np.arange(n * k) % 11).astype(np.float32) / np.float32(11.0) - np.float32(0.5)).reshape(n, k))
+    got = O.ref_bf16_gemm_nt(a, b, threads=2)
+    want = O.bf16_to_f32_array(a).astype(np.float64) @ O.bf16_to_f32_array(b).astype(np.float64).T
+    assert np.allclose(got, want.astype(np.float32), rtol=2e-7, atol=1e-9)
+    assert np.array_equal(got, O.ref_bf16_gemm_nt(a, b, threads=1))
+
+
 def test_silu_mul_restatement_tracks_the_formula():
     # cuda/layout.rs:231 computes g / (1 + exp(-g)) * u in f32 with the device's fast exponential and rounds to bf16;
     # the restatement's explicit exponential must land on the bf16 nearest the f64 value, or its neighbour
