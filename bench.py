@@ -255,8 +255,8 @@ class DenseWork:
 class MoeWork:
     """Expert-parallel contiguous grouped GEMM pair (see the module docstring)."""
 
-    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer"):
-        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel
+    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer", chunks=1, blocks_per_sm=2):
+        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel, PipelinedPeerMoe
         self.torch, self.dg, self.ctx, self.dev, self.world = torch, dg, ctx, dev, world
         c = self.c = dict(MOE)
         self.local_e = local_e = c["experts"] // world
@@ -284,10 +284,15 @@ class MoeWork:
         self.xq, self.xsf = dg.cast_bf16_to_fp8_sf_dev(ctx, x, c["hidden"], tokens, c["hidden"], 128)
         del x
         # rows travel through peer memory (kernels of the library) unless the peers cannot be mapped; every rank must agree
-        self.peer, self.exchange_note = None, "nccl all_to_all_single"
+        self.peer, self.pipe, self.chunks, self.exchange_note = None, None, max(1, chunks), "nccl all_to_all_single"
         if exchange == "peer":
             try:
-                self.peer = PeerExpertParallel(ctx, c["experts"], c["topk"], tokens, c["hidden"], c["down_n"])
+                if self.chunks > 1:
+                    self.pipe = PipelinedPeerMoe(ctx, c["experts"], c["topk"], tokens, c["hidden"], c["down_n"], self.chunks,
+                                                 blocks_per_sm=blocks_per_sm)
+                    self.peer = self.pipe.exchanges[0]
+                else:
+                    self.peer = PeerExpertParallel(ctx, c["experts"], c["topk"], tokens, c["hidden"], c["down_n"])
                 ok = 1
             except dg.DgError as e:
                 ok, self.exchange_note = 0, f"nccl all_to_all_single (peer mapping failed: {e})"
@@ -296,13 +301,18 @@ class MoeWork:
                 dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
                 ok = int(agreed.item())
             if not ok and self.peer is not None:
-                self.peer.close()
-                self.peer, self.exchange_note = None, "nccl all_to_all_single (a peer could not be mapped)"
+                (self.pipe or self.peer).close()
+                self.peer, self.pipe, self.exchange_note = None, None, "nccl all_to_all_single (a peer could not be mapped)"
         if self.peer is not None:
             cap = self.peer.capacity
             self.exchange_note = "peer-memory stores/loads (library kernels) + count all-gather" if world > 1 else "none (local arena)"
-            self.h = torch.empty((cap, c["gate_up_n"]), dtype=torch.bfloat16, device=dev)
-            self.act = (torch.empty((cap, c["down_k"]), dtype=torch.uint8, device=dev), dg.alloc_sf(ctx, cap, c["down_k"], 128))
+            if self.pipe is not None:
+                self.exchange_note += f"; {self.chunks} token micro-batches, exchange of one overlapping the GEMMs of another"
+            # per micro-batch: gate/up output and the quantised activation (capacity rows each)
+            self.bufs = {id(pe): (torch.empty((cap, c["gate_up_n"]), dtype=torch.bfloat16, device=dev),
+                                  (torch.empty((cap, c["down_k"]), dtype=torch.uint8, device=dev), dg.alloc_sf(ctx, cap, c["down_k"], 128)))
+                         for pe in (self.pipe.exchanges if self.pipe is not None else [self.peer])}
+            self.h, self.act = self.bufs[id(self.peer)]
         else:
             self.ep = ExpertParallel(c["experts"], c["topk"], DeviceRowOps(ctx))
         self.w1 = dg.LpOperand(w1q, w1sf, local_e * c["gate_up_n"], c["hidden"], c["hidden"])
@@ -310,8 +320,8 @@ class MoeWork:
         self.flops_per_row = 2.0 * (c["gate_up_n"] * c["hidden"] + c["down_n"] * c["down_k"])
         self.rows = 0
         if self.peer is not None:
-            # pair ranking, chunk scan, layout, dispatch, 2 GEMMs, SiLU-mul quantiser, combine
-            self.launches = 8
+            # per micro-batch: pair ranking, chunk scan, layout, dispatch, 2 GEMMs, SiLU-mul quantiser, combine
+            self.launches = 8 * self.chunks
         else:
             # pack, unpack, 2 x (group-end kernel, scan kernel, GEMM), SiLU-mul quantiser, combine, plus the result gather when rows travel
             self.launches = 10 + (1 if world > 1 else 0)
@@ -323,13 +333,12 @@ class MoeWork:
         xsf = self.xsf if xsf is None else xsf
         topi = self.topi if topi is None else topi
         topw = self.topw if topw is None else topw
+        if self.pipe is not None:
+            return self.pipe.run(topi, xq, xsf, topw, self.experts_compute)
         if self.peer is not None:
             pe = self.peer
             a_op, ends = pe.dispatch(topi, xq, xsf)
-            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(self.h, c["gate_up_n"]), self.local_e)
-            dg.silu_mul_cast_fp8_sf_dev(ctx, self.h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=self.act)
-            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, dg.LpOperand(self.act[0], self.act[1], pe.capacity, c["down_k"], c["down_k"]), ends,
-                                                          self.w2, dg.Sm100Out.Bf16(pe.result, c["down_n"]), self.local_e)
+            self.experts_compute(pe, a_op, ends)
             return pe.combine(topw)
         plan = self.ep.plan(topi)
         a, a_sf = self.ep.dispatch(plan, xq, xsf, c["hidden"])
@@ -345,8 +354,20 @@ class MoeWork:
         self.rows, self.plan = plan.n_recv, plan
         return out
 
+    def experts_compute(self, pe, a_op, ends):
+        """gate/up grouped GEMM, silu(gate) * up quantised for the down projection (the bf16 activation never touches memory),
+        down grouped GEMM into the buffer the combine reads."""
+        dg, c, ctx = self.dg, self.c, self.ctx
+        h, act = self.bufs[id(pe)]
+        dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(h, c["gate_up_n"]), self.local_e)
+        dg.silu_mul_cast_fp8_sf_dev(ctx, h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=act)
+        dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, dg.LpOperand(act[0], act[1], pe.capacity, c["down_k"], c["down_k"]), ends,
+                                                      self.w2, dg.Sm100Out.Bf16(pe.result, c["down_n"]), self.local_e)
+
     def routed_rows(self):
         """Valid arena rows of this rank in the last step (a host read, outside any timed region)."""
+        if self.pipe is not None:
+            return self.pipe.routed_rows()
         return int(self.peer.totals[1].item()) if self.peer is not None else self.rows
 
     def e2e_setup(self):
@@ -366,7 +387,15 @@ class MoeWork:
         torch, dg, c = self.torch, self.dg, self.c
         if self.peer is not None:
             pe = self.peer
-            a_op, ends = pe.dispatch(self.topi, self.xq, self.xsf)
+            if self.pipe is not None:
+                # one micro-batch on its own (all ranks take this branch together); rows reported are that micro-batch's
+                torch.cuda.synchronize()
+                t1 = self.pipe.chunk_tokens
+                with torch.cuda.stream(self.pipe.side):
+                    a_op, ends = pe.dispatch(self.topi[:t1], self.xq[:t1], self.xsf, dg.sf_aligned_rows(self.tokens))
+                self.pipe.side.synchronize()
+            else:
+                a_op, ends = pe.dispatch(self.topi, self.xq, self.xsf)
             times = []
             for _ in range(6):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -375,6 +404,11 @@ class MoeWork:
                 e1.record()
                 torch.cuda.synchronize()
                 times.append(e0.elapsed_time(e1))
+            if self.pipe is not None:
+                with torch.cuda.stream(self.pipe.side):
+                    pe.combine(self.topw[:self.pipe.chunk_tokens])
+                self.pipe.side.synchronize()
+                return statistics.median(times[1:]), int(pe.totals[1].item())
             pe.combine(self.topw)        # keeps the ranks' dispatch / combine fences paired
             return statistics.median(times[1:]), self.routed_rows()
         plan = self.ep.plan(self.topi)
@@ -517,6 +551,10 @@ def main():
     ap.add_argument("--moe-experts", type=int, default=None, help="moe_ep: total experts (default 256); 32 gives one rank of an 8-GPU job")
     ap.add_argument("--ep", default="peer", choices=["peer", "nccl"],
                     help="how MoE rows travel between ranks: peer-memory kernels of the library (default) or NCCL all-to-all")
+    ap.add_argument("--moe-chunks", type=int, default=1,
+                    help="token micro-batches of the MoE step whose exchange overlaps the other micro-batches' GEMMs (measured slower "
+                         "than 1 on 2 and 4 GPUs: the GEMMs lose more to the exchange kernels sharing their SMs than the overlap returns)")
+    ap.add_argument("--ep-blocks-per-sm", type=int, default=2, help="grid bound of the exchange kernels when they run beside the GEMMs")
     ap.add_argument("--only", default=None, help="M,N,K: run just this dense GEMM (profiling captures); implies --workload dense_fp8")
     args = ap.parse_args()
     if args.only:
@@ -553,7 +591,8 @@ def main():
 
     # ---- build the workload (untimed): operands resident in HBM, quantised by the library's own kernels
     dense = DenseWork(torch, dg, ctx, dev, 1000 + rank) if args.workload in ("dsv3", "dense_fp8") else None
-    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep) if args.workload in ("dsv3", "moe_ep") else None
+    chunks = max(1, args.moe_chunks)
+    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep, chunks, args.ep_blocks_per_sm) if args.workload in ("dsv3", "moe_ep") else None
     ctx.sync()
 
     def step(record=None):

@@ -122,8 +122,8 @@ _ep_hist_words = _proto("dg_ep_block_hist_words", _sz, _u32, _u32)
 _ep_count = _proto("dg_ep_count", C.c_int, _vp, _vp, _u32, _u32, _vp, _vp, _vp)
 _ep_layout = _proto("dg_ep_layout", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp)
 _ep_dispatch = _proto("dg_ep_dispatch", C.c_int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _u32, _u32, _vp, _vp, _u32,
-                      _u32, _vp)
-_ep_combine = _proto("dg_ep_combine", C.c_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _sz, _u32, _vp, _sz)
+                      _u32, _vp, _u32)
+_ep_combine = _proto("dg_ep_combine", C.c_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _sz, _u32, _vp, _sz, _u32)
 _expire_wait = _proto("dg_debug_expire_wait", C.c_int, _vp, _u32)
 _set_mk = _proto("dg_set_mk_alignment_for_contiguous_layout", C.c_int, _u32)
 _get_mk = _proto("dg_get_mk_alignment_for_contiguous_layout", _u32)
@@ -257,6 +257,26 @@ def fp8_fp4_gemm_dev(ctx: DgContext, a: LpOperand, b: LpOperand, out: Sm100Out, 
     """ops_sm100.rs:719"""
     ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
     _check(_gemm(ctx._h, C.byref(ca), C.byref(cb), C.byref(co), C.byref(ce)))
+
+
+def fp4_gemm_packed_dev(ctx, a_data: torch.Tensor, a_sf: torch.Tensor, b_data: torch.Tensor, b_sf: torch.Tensor, out: torch.Tensor,
+                        m: int, n: int, k: int):
+    """ops_sm100.rs:1693: MXFP4 GEMM over pre-quantised operands (packed e2m1 + per-32 UE8M0 words), bf16 output (m, n)."""
+    fp8_fp4_gemm_dev(ctx, LpOperand(a_data, a_sf, m, k, k, 4, 32), LpOperand(b_data, b_sf, n, k, k, 4, 32), Sm100Out.Bf16(out, n))
+
+
+def fp4_gemm_nt_native(ctx, a_bf16: torch.Tensor, b_bf16: torch.Tensor, m: int, n: int, k: int,
+                       sf_rule: int = SF_RULE_REFERENCE_CPU) -> torch.Tensor:
+    """ops_sm100.rs:1646: host bf16 tensors in, host bf16 result out: upload, quantise both operands to packed e2m1 +
+    UE8M0 per 32, run the MXF4 kernel, download."""
+    dev = torch.device(f"cuda:{ctx.ordinal}")
+    a_dev, b_dev = a_bf16.reshape(m, k).to(dev), b_bf16.reshape(n, k).to(dev)
+    a_data, a_sf = cast_bf16_to_fp4_packed_sf_dev(ctx, a_dev, k, m, k, 1, sf_rule)
+    b_data, b_sf = cast_bf16_to_fp4_packed_sf_dev(ctx, b_dev, k, n, k, 1, sf_rule)
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    fp4_gemm_packed_dev(ctx, a_data, a_sf, b_data, b_sf, out, m, n, k)
+    ctx.sync()
+    return out.cpu()
 
 
 def bf16_gemm_dev(ctx, a: torch.Tensor, a_ld: int, m: int, b: torch.Tensor, b_ld: int, n: int, k: int, out, epi=None):
@@ -541,15 +561,17 @@ def ep_layout_dev(ctx, all_counts, world, rank, num_experts, alignment, capacity
 
 
 def ep_dispatch_dev(ctx, expert_of_pair, local_rank, block_base, pair_base, pairs, topk, num_experts, world, data, k, sf, sf_stride, sf_cols,
-                    peer_data, peer_sf, peer_sf_stride, capacity, pos_of_pair):
+                    peer_data, peer_sf, peer_sf_stride, capacity, pos_of_pair, max_blocks=0):
     _check(_ep_dispatch(ctx._h, _vp(expert_of_pair.data_ptr()), _vp(local_rank.data_ptr()), _vp(block_base.data_ptr()),
                         _vp(pair_base.data_ptr()), pairs, topk, num_experts, world, _vp(data.data_ptr()), k, _vp(sf.data_ptr()), sf_stride,
-                        sf_cols, _vp(peer_data.data_ptr()), _vp(peer_sf.data_ptr()), peer_sf_stride, capacity, _vp(pos_of_pair.data_ptr())))
+                        sf_cols, _vp(peer_data.data_ptr()), _vp(peer_sf.data_ptr()), peer_sf_stride, capacity, _vp(pos_of_pair.data_ptr()),
+                        max_blocks))
 
 
-def ep_combine_dev(ctx, expert_of_pair, pos_of_pair, weights, tokens, topk, num_experts, world, peer_rows, pitch, n, out, out_pitch):
+def ep_combine_dev(ctx, expert_of_pair, pos_of_pair, weights, tokens, topk, num_experts, world, peer_rows, pitch, n, out, out_pitch,
+                   max_blocks=0):
     _check(_ep_combine(ctx._h, _vp(expert_of_pair.data_ptr()), _vp(pos_of_pair.data_ptr()), _vp(weights.data_ptr()), tokens, topk,
-                       num_experts, world, _vp(peer_rows.data_ptr()), pitch, n, _vp(out.data_ptr()), out_pitch))
+                       num_experts, world, _vp(peer_rows.data_ptr()), pitch, n, _vp(out.data_ptr()), out_pitch, max_blocks))
 
 
 def debug_expire_wait(ctx, limit_us: int = 1000):

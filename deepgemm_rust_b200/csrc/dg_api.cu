@@ -1031,7 +1031,7 @@ int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32
 int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* local_rank, const uint32_t* block_base, const uint32_t* pair_base,
                    uint32_t pairs, uint32_t topk, uint32_t num_experts, uint32_t world, const uint8_t* data, uint32_t k, const uint32_t* sf,
                    uint32_t sf_stride, uint32_t sf_cols, void* const* peer_data, void* const* peer_sf, uint32_t peer_sf_stride,
-                   uint32_t capacity, int32_t* pos_of_pair) {
+                   uint32_t capacity, int32_t* pos_of_pair, uint32_t max_blocks) {
     if (!ctx || !expert_of_pair || !local_rank || !block_base || !pair_base || !data || !sf || !peer_data || !peer_sf || !pos_of_pair)
         return fail(DG_ERR_SHAPE, "null argument");
     if (k % 16 || !aligned16(data)) return fail(DG_ERR_SHAPE, "k and the token rows must be multiples of 16 bytes");
@@ -1047,13 +1047,16 @@ int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* lo
     p.pairs = pairs; p.topk = topk; p.k = k; p.sf_cols = sf_cols; p.sf_stride = sf_stride; p.peer_sf_stride = peer_sf_stride;
     p.num_experts = num_experts; p.experts_per_rank = num_experts / world; p.capacity = capacity;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
-    dg::dg_ep_dispatch_kernel<<<ceil_div(pairs, 8), 256, 0, ctx->stream>>>(p);
+    uint32_t blocks = ceil_div(pairs, 8);
+    if (max_blocks != 0 && blocks > max_blocks) blocks = max_blocks;
+    dg::dg_ep_dispatch_kernel<<<blocks, 256, 0, ctx->stream>>>(p);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }
 
 int dg_ep_combine(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* pos_of_pair, const float* weights, uint32_t tokens, uint32_t topk,
-                  uint32_t num_experts, uint32_t world, const void* const* peer_rows, size_t pitch, uint32_t n, uint16_t* out, size_t out_pitch) {
+                  uint32_t num_experts, uint32_t world, const void* const* peer_rows, size_t pitch, uint32_t n, uint16_t* out, size_t out_pitch,
+                  uint32_t max_blocks) {
     if (!ctx || !expert_of_pair || !pos_of_pair || !weights || !peer_rows || !out) return fail(DG_ERR_SHAPE, "null argument");
     if (n % 8 || pitch % 8 || out_pitch % 8 || !aligned16(out)) return fail(DG_ERR_SHAPE, "n and pitches must be multiples of 8 elements");
     if (world == 0 || num_experts % world != 0) return fail(DG_ERR_SHAPE, "num_experts (%u) must be a multiple of world (%u)", num_experts, world);
@@ -1065,7 +1068,9 @@ int dg_ep_combine(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* pos
     p.tokens = tokens; p.topk = topk; p.n = n; p.experts_per_rank = num_experts / world;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     const uint64_t threads = static_cast<uint64_t>(tokens) * (n / 8);
-    dg::dg_ep_combine_kernel<<<static_cast<uint32_t>((threads + 255) / 256), 256, 0, ctx->stream>>>(p);
+    uint32_t blocks = static_cast<uint32_t>((threads + 255) / 256);
+    if (max_blocks != 0 && blocks > max_blocks) blocks = max_blocks;
+    dg::dg_ep_combine_kernel<<<blocks, 256, 0, ctx->stream>>>(p);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }

@@ -194,6 +194,9 @@ __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __re
     }
 }
 
+struct EpDispatchParams;
+DG_DEVICE void ep_dispatch_pair(const EpDispatchParams& p, uint64_t pair, uint32_t lane);
+
 struct EpDispatchParams {
     const int32_t* expert_of_pair;   // (pairs)
     const int32_t* local_rank;       // (pairs)
@@ -207,11 +210,7 @@ struct EpDispatchParams {
     uint32_t pairs, topk, k, sf_cols, sf_stride, peer_sf_stride, num_experts, experts_per_rank, capacity;
 };
 
-// One warp per (token, j) pair.
-__global__ void __launch_bounds__(256) dg_ep_dispatch_kernel(const EpDispatchParams p) {
-    const uint32_t lane = threadIdx.x % 32;
-    const uint64_t pair = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
-    if (pair >= p.pairs) return;
+DG_DEVICE void ep_dispatch_pair(const EpDispatchParams& p, uint64_t pair, uint32_t lane) {
     const int32_t lr = __ldg(p.local_rank + pair);
     if (lr < 0) { if (lane == 0) p.pos_of_pair[pair] = -1; return; }
     const uint32_t e = static_cast<uint32_t>(__ldg(p.expert_of_pair + pair));
@@ -233,6 +232,16 @@ __global__ void __launch_bounds__(256) dg_ep_dispatch_kernel(const EpDispatchPar
         dsf[static_cast<size_t>(w) * p.peer_sf_stride + row] = __ldg(p.sf + static_cast<size_t>(w) * p.sf_stride + tok);
 }
 
+
+// One warp per (token, j) pair; the grid may be smaller than the pair count (warps stride over the pairs), which
+// lets a caller leave room on every SM for a kernel running beside this one.
+__global__ void __launch_bounds__(256) dg_ep_dispatch_kernel(const EpDispatchParams p) {
+    const uint32_t lane = threadIdx.x % 32;
+    const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x / 32);
+    for (uint64_t pair = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; pair < p.pairs; pair += warps)
+        ep_dispatch_pair(p, pair, lane);
+}
+
 struct EpCombineParams {
     const int32_t* expert_of_pair;    // (tokens, topk)
     const int32_t* pos_of_pair;       // (tokens, topk) result row on the owner, < 0 skips the term
@@ -247,8 +256,8 @@ struct EpCombineParams {
 // chain as dg_moe_combine_kernel, reading each term from the rank that computed it.  One thread owns 8 columns.
 __global__ void __launch_bounds__(256) dg_ep_combine_kernel(const EpCombineParams p) {
     const uint32_t chunks = p.n / 8;
-    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= static_cast<uint64_t>(p.tokens) * chunks) return;
+    const uint64_t total = static_cast<uint64_t>(p.tokens) * chunks, stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     const uint32_t t = static_cast<uint32_t>(i / chunks), c = static_cast<uint32_t>(i % chunks);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (uint32_t j0 = 0; j0 < p.topk; j0 += 4) {
@@ -288,6 +297,7 @@ __global__ void __launch_bounds__(256) dg_ep_combine_kernel(const EpCombineParam
     o.z = pack_bf16x2(acc[4], acc[5]);
     o.w = pack_bf16x2(acc[6], acc[7]);
     reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.out_pitch)[c] = o;
+    }
 }
 
 }  // namespace dg

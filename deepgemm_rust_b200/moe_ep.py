@@ -211,6 +211,7 @@ class PeerExpertParallel:
         self._fence_word = torch.zeros(1, **i32)
         self._experts = None
         self._tokens = 0
+        self.max_blocks = 0                           # grid bound of the dispatch / combine kernels (0: as many blocks as items)
         self._fence()                                 # every rank's buffers are mapped and cleared before the first step
 
     def _fence(self):
@@ -222,8 +223,10 @@ class PeerExpertParallel:
         """The arena as the grouped GEMMs' A: `capacity` rows, of which the group table bounds the work."""
         return self.dg.LpOperand(self.arena, self.arena_sf, self.capacity, self.hidden, self.hidden, 8, self.gran)
 
-    def dispatch(self, topk_idx: torch.Tensor, xq: torch.Tensor, xsf: torch.Tensor):
-        """This rank's e4m3 token rows + packed scales -> arena rows on the expert ranks.  Returns (operand, group_ends)."""
+    def dispatch(self, topk_idx: torch.Tensor, xq: torch.Tensor, xsf: torch.Tensor, sf_stride: Optional[int] = None):
+        """This rank's e4m3 token rows + packed scales -> arena rows on the expert ranks.  Returns (operand, group_ends).
+        sf_stride: words between two scale columns of xsf (default: the packed layout of exactly these tokens); a larger
+        value lets xsf point into the scale words of a longer token batch."""
         dg, ctx = self.dg, self.ctx
         tokens, topk = topk_idx.shape
         pairs = tokens * topk
@@ -237,17 +240,19 @@ class PeerExpertParallel:
         dg.ep_layout_dev(ctx, self._all_counts, self.world, self.rank, self.num_experts, self.alignment, self.capacity, self._pair_base,
                          self.group_ends, self.totals)
         dg.ep_dispatch_dev(ctx, self._experts, self._local_rank, self._block_hist, self._pair_base, pairs, topk, self.num_experts, self.world,
-                           xq, self.hidden, xsf, dg.sf_aligned_rows(tokens), self.sf_cols, self._peer_data, self._peer_sf, self.sf_stride,
-                           self.capacity, self.pos_of_pair)
+                           xq, self.hidden, xsf, sf_stride or dg.sf_aligned_rows(tokens), self.sf_cols, self._peer_data, self._peer_sf, self.sf_stride,
+                           self.capacity, self.pos_of_pair, self.max_blocks)
         self._fence()
         return self.operand(), self.group_ends
 
-    def combine(self, weights: torch.Tensor) -> torch.Tensor:
-        """`result` rows of all ranks (the last grouped GEMM wrote them) -> per-token weighted sums on the token ranks."""
+    def combine(self, weights: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """`result` rows of all ranks (the last grouped GEMM wrote them) -> per-token weighted sums on the token ranks
+        (written to `out` (tokens, out_n) bf16 if given)."""
         self._fence()
-        out = torch.empty((self._tokens, self.out_n), dtype=torch.bfloat16, device=self.device)
+        if out is None:
+            out = torch.empty((self._tokens, self.out_n), dtype=torch.bfloat16, device=self.device)
         self.dg.ep_combine_dev(self.ctx, self._experts, self.pos_of_pair, weights, self._tokens, self.topk, self.num_experts, self.world,
-                               self._peer_rows, self.out_n, self.out_n, out, self.out_n)
+                               self._peer_rows, self.out_n, self.out_n, out, self.out_n, self.max_blocks)
         return out
 
     def overflowed(self) -> bool:
@@ -268,3 +273,75 @@ class PeerExpertParallel:
         self.arena = self.arena_sf = self.result = None
         self.dg.peer_free(self.ctx, self._base)
         self._base = None
+
+
+class PipelinedPeerMoe:
+    """A MoE layer over `PeerExpertParallel` in `chunks` token micro-batches: the peer-memory dispatch and combine of one
+    micro-batch run on a second stream while the grouped GEMMs of another run on the caller's stream.
+
+    compute(exchange, a_op, group_ends) is the caller's expert computation for one micro-batch: it must enqueue, on the
+    compute context's stream, work that reads the arena operand and leaves the result rows in `exchange.result`.
+    Every micro-batch has its own exchange buffers, so nothing of one micro-batch is overwritten while another is in
+    flight; all collectives are issued from the exchange stream in the same order on every rank.  A token's output does
+    not depend on which micro-batch it travelled in (rows are independent in the GEMMs and the reduction order is the
+    token's own top-k order), so the result equals the unchunked step bit for bit.
+    """
+
+    def __init__(self, compute_ctx, num_experts: int, topk: int, max_tokens: int, hidden: int, out_n: int, chunks: int = 2, gran: int = 128,
+                 group: Optional[dist.ProcessGroup] = None, alignment: int = 128, blocks_per_sm: int = 2):
+        import deepgemm_rust_b200 as dg
+        self.dg, self.chunks = dg, chunks
+        self.compute_ctx = compute_ctx
+        self.device = torch.device(f"cuda:{compute_ctx.ordinal}")
+        self.chunk_tokens = (max_tokens + chunks - 1) // chunks
+        self.side = torch.cuda.Stream(device=self.device)
+        self.exchange_ctx = dg.DgContext(compute_ctx.ordinal, stream=self.side.cuda_stream)
+        with torch.cuda.stream(self.side):
+            self.exchanges = [PeerExpertParallel(self.exchange_ctx, num_experts, topk, self.chunk_tokens, hidden, out_n, gran, group, alignment)
+                              for _ in range(chunks)]
+        self.side.synchronize()
+        # the exchange kernels run beside a persistent GEMM that needs one block slot and most of the shared memory of
+        # every SM: two 256-thread blocks per SM move rows fast enough for NVLink and leave that slot free
+        for e in self.exchanges:
+            e.max_blocks = blocks_per_sm * compute_ctx.num_sms()
+        self.out_n = out_n
+
+    def run(self, topk_idx: torch.Tensor, xq: torch.Tensor, xsf: torch.Tensor, weights: torch.Tensor, compute) -> torch.Tensor:
+        dg = self.dg
+        tokens = topk_idx.shape[0]
+        main = torch.cuda.current_stream(self.device)
+        out = torch.empty((tokens, self.out_n), dtype=torch.bfloat16, device=self.device)
+        bounds = [(c * self.chunk_tokens, min(tokens, (c + 1) * self.chunk_tokens)) for c in range(self.chunks)]
+        bounds = [b for b in bounds if b[0] < b[1]]
+        sf_stride = dg.sf_aligned_rows(tokens)
+        self.side.wait_stream(main)                      # the inputs were produced on the caller's stream
+        landed, computed = [], []
+        with torch.cuda.stream(self.side):
+            for c, (t0, t1) in enumerate(bounds):
+                # a micro-batch's scale words are columns [t0, t1) of the packed (sf_cols, align4(tokens)) matrix: same stride, offset base
+                a_op, ends = self.exchanges[c].dispatch(topk_idx[t0:t1], xq[t0:t1], xsf.view(-1)[t0:], sf_stride)
+                ev = torch.cuda.Event()
+                ev.record(self.side)
+                landed.append((a_op, ends, ev))
+        for c in range(len(bounds)):
+            a_op, ends, ev = landed[c]
+            main.wait_event(ev)
+            compute(self.exchanges[c], a_op, ends)
+            done = torch.cuda.Event()
+            done.record(main)
+            computed.append(done)
+        with torch.cuda.stream(self.side):
+            for c, (t0, t1) in enumerate(bounds):
+                self.side.wait_event(computed[c])
+                self.exchanges[c].combine(weights[t0:t1], out[t0:t1])
+        main.wait_stream(self.side)
+        return out
+
+    def routed_rows(self) -> int:
+        return sum(int(e.totals[1].item()) for e in self.exchanges)
+
+    def close(self):
+        for e in self.exchanges:
+            e.close()
+        self.exchanges = []
+        self.exchange_ctx.close()

@@ -243,16 +243,19 @@ int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32
 /* moe.rs:176-206 (gather of token rows and scale rows into the grouped layout), across ranks: pair p's e4m3 row
  * (k bytes) and its sf_cols scale words go to row pos_of_pair[p] of the arena of the rank that owns its expert.
  * peer_data / peer_sf: device arrays of `world` pointers (every rank's arena (capacity, k) and its scale words
- * sf[c * peer_sf_stride + row]), entry `rank` being the local buffers.  Padding rows are not written. */
+ * sf[c * peer_sf_stride + row]), entry `rank` being the local buffers.  Padding rows are not written.
+ * max_blocks: 0 launches one warp per pair; a positive value bounds the grid (256-thread blocks striding over the
+ * pairs), e.g. 2 x the SM count to leave room on every SM for a GEMM running beside the exchange. */
 int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* local_rank, const uint32_t* block_base, const uint32_t* pair_base,
                    uint32_t pairs, uint32_t topk, uint32_t num_experts, uint32_t world, const uint8_t* data, uint32_t k, const uint32_t* sf,
                    uint32_t sf_stride, uint32_t sf_cols, void* const* peer_data, void* const* peer_sf, uint32_t peer_sf_stride,
-                   uint32_t capacity, int32_t* pos_of_pair);
+                   uint32_t capacity, int32_t* pos_of_pair, uint32_t max_blocks);
 /* moe.rs:314-360 (weighted scatter-accumulate and f32 -> bf16), across ranks and as a gather: out[t, :] =
  * bf16(sum_j weights[t, j] * rows_j[pos_of_pair[t, j], :]) with rows_j the result buffer (bf16, `pitch` elements per
- * row) of the rank owning expert_of_pair[t, j]; same arithmetic as dg_moe_combine. */
+ * row) of the rank owning expert_of_pair[t, j]; same arithmetic as dg_moe_combine.  max_blocks as for dg_ep_dispatch. */
 int dg_ep_combine(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* pos_of_pair, const float* weights, uint32_t tokens, uint32_t topk,
-                  uint32_t num_experts, uint32_t world, const void* const* peer_rows, size_t pitch, uint32_t n, uint16_t* out, size_t out_pitch);
+                  uint32_t num_experts, uint32_t world, const void* const* peer_rows, size_t pitch, uint32_t n, uint16_t* out, size_t out_pitch,
+                  uint32_t max_blocks);
 
 /* No counterpart in the reference (its device waits spin without bound, deepgemm/src/cuda/common.rs:74-85).
  * Self-test of the bounded wait all kernels here use: launches one warp that waits, for at most limit_us, on a

@@ -12,7 +12,7 @@ import torch
 
 import deepgemm_rust_b200 as dg
 from oracle import oracle as O
-from tests.helpers import dev, fp4_operand, fp8_operand_1d, fp8_operand_2d, sample_indices, to_f32
+from tests.helpers import dev, fp4_operand, fp8_operand_1d, fp8_operand_2d, randn_bf16, sample_indices, to_f32
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3          # contract
@@ -390,6 +390,18 @@ def test_dense_mixed_fp8_fp4(ctx, m, n, k, a_bits, b_bits, gran8):
     rows, cols = np.arange(m, dtype=np.uint32), np.arange(n, dtype=np.uint32)
     want = O.lp_gemm_rows(aq, asf, a_bits, ga, 1, m, rows, bq, bsf, b_bits, gb, 1, n, cols, k)
     assert O.calc_diff(to_f32(d), want) <= TIGHT_F32
+
+
+def test_fp4_convenience_entry_points(ctx):
+    # ops_sm100.rs:1646 / :1693: bf16 host tensors -> quantise -> MXF4 GEMM -> bf16 host result; equals the oracle's
+    # quantiser followed by its f64 MXFP4 reference, to bf16 rounding
+    m, n, k = 96, 160, 640
+    a, b = randn_bf16(m, k, 91), randn_bf16(n, k, 92)
+    out = dg.fp4_gemm_nt_native(ctx, torch.from_numpy(a.view(np.int16)).view(torch.bfloat16), torch.from_numpy(b.view(np.int16)).view(torch.bfloat16), m, n, k)
+    aq, asf = O.cast_bf16_to_fp4_packed_sf(a, k, 1, 0)
+    bq, bsf = O.cast_bf16_to_fp4_packed_sf(b, k, 1, 0)
+    want = O.mxfp4_gemm_reference(aq, asf, m, bq, bsf, n, k, threads=O.max_threads())
+    assert O.calc_diff(to_f32(out), want) <= TIGHT_BF16
 
 
 def test_m_grouped_mxfp4(ctx):

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import deepgemm_rust_b200 as dg
-from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel
+from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel, PipelinedPeerMoe
 from oracle import oracle as O
 from tests.helpers import dev, fp8_operand_1d, fp8_operand_2d, to_f32
 
@@ -211,3 +211,34 @@ def test_peer_exchange_reports_overflow(ctx):
         assert np.array_equal(pos[:128, 1], 256 + np.arange(128)) and np.all(pos[128:, 1] == -1)
     finally:
         pe.close()
+
+
+def test_pipelined_micro_batches_equal_the_single_batch(ctx):
+    # exchange on a second stream, three token micro-batches (the last one shorter): every token's output must equal
+    # the unchunked step bit for bit
+    experts, topk, tokens, hidden, n = 8, 2, 500, 512, 256
+    g = torch.Generator().manual_seed(33)
+    topw, topi = torch.softmax(torch.randn((tokens, experts), generator=g), -1).topk(topk, dim=-1)
+    _, xq, xsf = fp8_operand_1d(tokens, hidden, 51)
+    _, wq, wsf, _ = fp8_operand_2d(experts * n, hidden, 52, experts)
+    w_op = dg.LpOperand(dev(wq), dev(wsf), experts * n, hidden, hidden)
+    topi_d, topw_d, xq_d, xsf_d = topi.cuda(), topw.cuda().contiguous(), dev(xq), dev(xsf)
+
+    def compute(pe, a_op, ends):
+        dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, w_op, dg.Sm100Out.Bf16(pe.result, n), experts)
+
+    pe = PeerExpertParallel(ctx, experts, topk, tokens, hidden, n)
+    a_op, ends = pe.dispatch(topi_d, xq_d, xsf_d)
+    compute(pe, a_op, ends)
+    want = pe.combine(topw_d).view(torch.int16).cpu().numpy()
+    ctx.sync()
+    pe.close()
+    pipe = PipelinedPeerMoe(ctx, experts, topk, tokens, hidden, n, chunks=3)
+    try:
+        for _ in range(2):
+            out = pipe.run(topi_d, xq_d, xsf_d, topw_d, compute)
+            torch.cuda.synchronize()
+            assert np.array_equal(out.view(torch.int16).cpu().numpy(), want)
+            assert pipe.routed_rows() == tokens * topk
+    finally:
+        pipe.close()

@@ -20,7 +20,7 @@ def _rank_main(rank, world, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import deepgemm_rust_b200 as dg
-        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel
+        from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel, PipelinedPeerMoe
         from oracle import oracle as O
         dev = torch.device("cuda", rank)
         ctx = dg.DgContext(rank)
@@ -67,6 +67,18 @@ def _rank_main(rank, world, port, results):
             totals = pe.totals.cpu().numpy()
             ok = ok and int(totals[1]) == plan.n_recv and int(totals[0]) == plan.m_pad
         pe.close()
+        # and in token micro-batches whose exchange overlaps the other micro-batch's GEMM
+        w_local = dg.LpOperand(wq_local, wsf_local, local * n, k, k)
+
+        def compute(ex, a_op, ends):
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, w_local, dg.Sm100Out.Bf16(ex.result, n), local)
+
+        pipe = PipelinedPeerMoe(ctx, experts, topk, tokens, k, n, chunks=2)
+        for _ in range(2):
+            out3 = pipe.run(topi, xq, xsf, topw, compute)
+            torch.cuda.synchronize()
+            ok = ok and bool(np.array_equal(out3.view(torch.int16).cpu().numpy().view(np.uint16), want))
+        pipe.close()
         results[rank] = ok
         ctx.close()
     finally:
