@@ -595,23 +595,30 @@ DGO_API void dgo_ref_bf16_gemm_nt(const uint16_t* a, uint32_t m, const uint16_t*
 /* SiLU-and-mul (cuda/layout.rs:218-233 as called from moe.rs:273-296): out[r,c] = bf16(silu(gate) * up) on a
  * (rows, 2n) gate|up matrix of bf16 bits, silu(g) = g / (1 + exp(-g)).  The reference's device code uses the
  * fast-math exponential, which no host function reproduces bit for bit; exp is therefore written out here
- * (and identically in the CUDA kernel) in correctly rounded f32 steps: n = rint(x * log2 e), r = x - n ln2 in
- * two parts, a degree-7 Taylor polynomial on |r| <= ln2/2, times 2^n; gate values below -88 give 0.  Parity unpinned: a test bounds the
- * distance to the f64 formula instead. */
+ * (and identically in the CUDA kernel) in correctly rounded f32 steps: the gate is clamped to [-87, 30];
+ * n = rint(-g log2 e) is read from the low mantissa bits of fma(g, -log2 e, 1.5 * 2^23); r = -g - n ln2 with
+ * ln 2 in two parts; exp(r) - 1 is a degree-5 Taylor polynomial on |r| <= ln2/2; 2^n is applied by adding n to
+ * the exponent field; 1 / (1 + exp(-g)) by three Newton steps x <- x (2 - d x) from the estimate
+ * 0x7EF311C7 - bits(d); silu = g * that; gates below -87 give 0.
+ * Parity unpinned: a test bounds the distance to the f64 formula instead. */
 static float dgo_silu_mul_one(float g, float u) {
-    float x = fminf(fmaxf(-g, -87.0f), 88.0f);
-    float n = rintf(x * 1.44269504f);
-    float r = fmaf(n, -0.693145752f, x);
+    float gc = fminf(fmaxf(g, -87.0f), 30.0f);
+    float t = fmaf(gc, -1.44269504f, 12582912.0f);
+    float n = t + -12582912.0f;
+    float r = fmaf(n, -0.693145752f, -gc);
     r = fmaf(n, -1.42860677e-6f, r);
-    float q = 1.0f / 5040.0f;
-    q = fmaf(q, r, 1.0f / 720.0f);
-    q = fmaf(q, r, 1.0f / 120.0f);
-    q = fmaf(q, r, 1.0f / 24.0f);
+    float q = fmaf(1.0f / 120.0f, r, 1.0f / 24.0f);
     q = fmaf(q, r, 1.0f / 6.0f);
     q = fmaf(q, r, 0.5f);
     q = fmaf(q, r * r, r);
-    float e = (q + 1.0f) * u2f((uint32_t)((int32_t)n + 127) << 23);
-    float silu = -g > 88.0f ? 0.0f : g / (1.0f + e);   /* |g exp(g)| < 5e-37 there */
+    float s = q + 1.0f;
+    float e = u2f(f2u(s) + (f2u(t) << 23));
+    float d = 1.0f + e;
+    float x = u2f(0x7EF311C7u - f2u(d));
+    x = x * fmaf(-d, x, 2.0f);
+    x = x * fmaf(-d, x, 2.0f);
+    x = x * fmaf(-d, x, 2.0f);
+    float silu = g < -87.0f ? 0.0f : g * x;   /* |g exp(g)| < 2e-36 below -87 */
     float act = silu * u;
     return dgo_bf16_to_f32(dgo_f32_to_bf16(act));
 }
