@@ -344,6 +344,28 @@ struct Problem {
     bool bf16 = false;     // operands are bf16 rows described as 2k bytes each; no scale factors (dg_bf16_gemm)
 };
 
+// DG_PDL=0 launches every kernel fully serialised (for comparisons and debugging).
+bool pdl_enabled() {
+    static const bool on = [] { const char* v = getenv("DG_PDL"); return !(v && strcmp(v, "0") == 0); }();
+    return on;
+}
+
+template <bool kBf16>
+cudaError_t launch_reduce(uint32_t blocks, cudaStream_t stream, const float* partial, uint32_t splits, uint32_t m, uint32_t n, uint32_t pitch,
+                          float alpha, void* out, uint32_t out_ld) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, dg::dg_splitk_reduce_kernel<kBf16>, partial, splits, m, n, pitch, alpha, out, out_ld);
+}
+
 template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
 cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
     auto kernel = dg::dg_gemm_kernel<kFmt, kOut, kCtas>;
@@ -362,13 +384,16 @@ cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem,
     cfg.blockDim = dim3(dg::kNumThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kCtas;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // the kernel waits for its predecessor itself (griddep_wait) after its set-up: let the two overlap
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, p, maps[0], maps[1], maps[2], maps[3], maps[4]);
 }
 
@@ -551,11 +576,8 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         const uint64_t threads = static_cast<uint64_t>(pr.m) * ceil_div(pr.n, 4);
         const uint32_t blocks = static_cast<uint32_t>((threads + 255) / 256);
         const float alpha = e.has_alpha ? e.alpha : 1.0f;
-        if (out->kind == DG_OUT_BF16)
-            dg::dg_splitk_reduce_kernel<true><<<blocks, 256, 0, ctx->stream>>>(ctx->splitk_ws, splits, pr.m, pr.n, ws_pitch, alpha, out->buf, out->ld);
-        else
-            dg::dg_splitk_reduce_kernel<false><<<blocks, 256, 0, ctx->stream>>>(ctx->splitk_ws, splits, pr.m, pr.n, ws_pitch, alpha, out->buf, out->ld);
-        ce = cudaGetLastError();
+        ce = out->kind == DG_OUT_BF16 ? launch_reduce<true>(blocks, ctx->stream, ctx->splitk_ws, splits, pr.m, pr.n, ws_pitch, alpha, out->buf, out->ld)
+                                      : launch_reduce<false>(blocks, ctx->stream, ctx->splitk_ws, splits, pr.m, pr.n, ws_pitch, alpha, out->buf, out->ld);
     }
     if (ce != cudaSuccess) return fail(DG_ERR_DRIVER, "kernel launch failed: %s", cudaGetErrorString(ce));
     return DG_OK;

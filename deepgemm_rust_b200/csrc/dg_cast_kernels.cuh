@@ -277,6 +277,8 @@ __global__ void __launch_bounds__(1024) dg_group_ends_scan_kernel(uint32_t* ends
 template <bool kBf16>
 __global__ void __launch_bounds__(256) dg_splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, uint32_t m, uint32_t n,
                                                                uint32_t pitch, float alpha, void* __restrict__ out, uint32_t out_ld) {
+    griddep_wait();                // launched beside the tail of the GEMM that writes the partials
+    griddep_launch_dependents();
     const uint32_t chunks = (n + 3) / 4;
     const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= static_cast<uint64_t>(m) * chunks) return;

@@ -264,6 +264,9 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     tc_fence_before();
     if constexpr (kCtas == 2) cluster_sync(); else __syncthreads();
     tc_fence_after();
+    // up to here nothing read or wrote global memory: the set-up above may overlap the previous kernel of the stream
+    griddep_wait();
+    griddep_launch_dependents();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_sfa = tmem_base + p.num_accum_stages * block_n;
     const uint32_t tmem_sfb = tmem_sfa + 4 * plan_a.words;

@@ -252,6 +252,14 @@ DG_DEVICE void umma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_de
     }
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may start while the
+// kernel before it in the stream is still running; griddep_wait() returns once that kernel has completed and its
+// memory is visible, so everything before the call (barrier set-up, TMEM allocation, descriptor prefetch) overlaps the
+// predecessor's tail and nothing after it can race with it.  griddep_launch_dependents() lets the next kernel in the
+// stream do the same with this one.  Both are no-ops for a kernel launched without the attribute.
+DG_DEVICE void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+DG_DEVICE void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Plain (not block-scaled) 16-bit UMMA: K = 16 elements = 32 bytes per instruction.
 template <int CTAS>
 DG_DEVICE void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
