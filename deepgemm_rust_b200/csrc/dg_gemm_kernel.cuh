@@ -495,19 +495,16 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 continue;
             }
 #endif
-            for (uint32_t s = 0; s < num_subs; ++s) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(taddr + s * 32, v);
-                tmem_ld_wait_x32(v);
-                if (s + 1 == num_subs) {
-                    // the accumulator is in registers: hand the TMEM stage back to the UMMA warp
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
-                        else mbar_arrive_remote(bar_tmem_empty + e, 0);
-                    }
+            // hand the TMEM stage back to the UMMA warp once its last columns are in registers
+            auto release_accumulator = [&]() {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
+                    else mbar_arrive_remote(bar_tmem_empty + e, 0);
                 }
+            };
+            auto process = [&](uint32_t (&v)[32], uint32_t s) {
                 const uint32_t sub_in_buf = s % kSubsPerBuf;
                 uint8_t* buf = buf0 + buf_idx * kEpiBufBytes;
                 if (sub_in_buf == 0) {
@@ -581,6 +578,23 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         tma_store_commit();
                     }
                     buf_idx ^= 1;
+                }
+            };
+            // two register sets: the TMEM load of the next 32 columns is in flight while the current ones are
+            // converted and staged
+            uint32_t va[32], vb[32];
+            tmem_ld_32x32b_x32(taddr, va);
+            for (uint32_t s = 0; s < num_subs; s += 2) {
+                tmem_ld_wait_x32(va);
+                const bool has_b = s + 1 < num_subs;
+                if (has_b) tmem_ld_32x32b_x32(taddr + (s + 1) * 32, vb);
+                else release_accumulator();
+                process(va, s);
+                if (has_b) {
+                    tmem_ld_wait_x32(vb);
+                    if (s + 2 < num_subs) tmem_ld_32x32b_x32(taddr + (s + 2) * 32, va);
+                    else release_accumulator();
+                    process(vb, s + 1);
                 }
             }
         }
