@@ -701,7 +701,7 @@ def main():
                         "frac": achieved / peak if achieved else None,
                         # dram__bytes_read.sum + dram__bytes_write.sum of this launch, one ncu capture
                         # (profiles/dg_gemm_kernel_fp8_M4096_N7168_K16384.md); algorithmic bytes are 2.447e8
-                        "traffic": 6.48e8 if DOMINANT == (4096, 7168, 16384) else None,
+                        "traffic": 5.37e8 if DOMINANT == (4096, 7168, 16384) else None,
                         "kernel": "dg_gemm_kernel<fp8, bf16 out, CTA pair>", "launch": f"dense M={m} N={n} K={k}",
                         "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} peaks (e4m3 issues at twice the bf16 rate)",
                         "frac_of_nominal_fp8_4500": achieved / 4500.0 if achieved else None}

@@ -143,9 +143,10 @@ struct Scheduler {
                 return false;
             }
             const uint32_t g = idx / per_group, r = idx - g * per_group;
-            // bands of 16 row-blocks, rows fastest inside a band: the tiles in flight at
-            // any moment form a compact patch, so A and B tiles are re-read from L2
-            constexpr uint32_t kBand = 16;
+            // bands of 2048 rows, rows fastest inside a band: the tiles in flight at any moment form a
+            // patch about as tall as it is wide (148 tiles of 128 x 224..256), which is what minimises the
+            // A rows plus B rows a wave pulls from DRAM, and a band's A rows stay in L2 for its next wave
+            const uint32_t kBand = 2048 / tile_m;
             const uint32_t per_band = kBand * num_n_blocks;
             const uint32_t band = r / per_band, in_band = r - band * per_band;
             const uint32_t first_m = band * kBand;
