@@ -555,6 +555,7 @@ def main():
                     help="token micro-batches of the MoE step whose exchange overlaps the other micro-batches' GEMMs (measured slower "
                          "than 1 on 2 and 4 GPUs: the GEMMs lose more to the exchange kernels sharing their SMs than the overlap returns)")
     ap.add_argument("--ep-blocks-per-sm", type=int, default=2, help="grid bound of the exchange kernels when they run beside the GEMMs")
+    ap.add_argument("--moe-tokens", type=int, default=None, help="moe_ep: tokens per rank (default 8192); smaller values for profiling captures")
     ap.add_argument("--only", default=None, help="M,N,K: run just this dense GEMM (profiling captures); implies --workload dense_fp8")
     args = ap.parse_args()
     if args.only:
@@ -564,6 +565,8 @@ def main():
         args.workload = "dense_fp8"
     if args.moe_experts:
         MOE["experts"] = args.moe_experts
+    if args.moe_tokens:
+        MOE["tokens_per_rank"] = args.moe_tokens
     if args.impl == "reference":
         run_reference(args)
         return
