@@ -66,3 +66,24 @@ def dev(arr, dtype=None):
     if dtype is not None:
         t = t.view(dtype)
     return t
+
+
+def peer_layout(all_counts, rank, alignment=128):
+    """numpy restatement of the arena layout every rank derives from the all-gathered (world, experts) pair counts:
+    groups sit on their owner in expert order, each starting at a multiple of the alignment, rows ordered by source
+    rank.  Returns (pair_base (experts), group_ends (experts / world), [rows in use here, valid rows here, largest arena])."""
+    all_counts = np.asarray(all_counts, dtype=np.int64)
+    world, experts = all_counts.shape
+    local = experts // world
+    rows_of = all_counts.sum(0)
+    before_me = all_counts[:rank].sum(0)
+    padded = (rows_of + alignment - 1) // alignment * alignment
+    start = np.zeros(experts, np.int64)
+    arena = np.zeros(world, np.int64)
+    for owner in range(world):
+        sl = slice(owner * local, (owner + 1) * local)
+        start[sl] = np.cumsum(padded[sl]) - padded[sl]
+        arena[owner] = padded[sl].sum()
+    mine = slice(rank * local, (rank + 1) * local)
+    group_ends = start[mine] + rows_of[mine]
+    return start + before_me, group_ends, [int(arena[rank]), int(rows_of[mine].sum()), int(arena.max())]

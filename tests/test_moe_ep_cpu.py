@@ -118,3 +118,39 @@ def test_expert_parallel_gloo(world):
             p.join(120)
             assert p.exitcode == 0
         assert dict(results) == {r: True for r in range(world)}
+
+
+def test_peer_layout_restatement_is_consistent():
+    # the numpy restatement the GPU tests hold the layout kernel to: arenas are disjoint unions of contiguous
+    # (expert, source rank) segments, groups start aligned, and on one rank it agrees with ExpertParallel.plan
+    from tests.helpers import peer_layout
+    rng = np.random.default_rng(3)
+    for world, experts in [(2, 8), (4, 32)]:
+        counts = rng.integers(0, 300, (world, experts))
+        counts[:, 1] = 0
+        local = experts // world
+        bases = [peer_layout(counts, r)[0] for r in range(world)]
+        for owner in range(world):
+            _, ends, totals = peer_layout(counts, owner)
+            taken = np.zeros(totals[0], bool)
+            prev_end = 0
+            for l in range(local):
+                e = owner * local + l
+                start = (prev_end + 127) // 128 * 128
+                row = start
+                for src in range(world):
+                    assert bases[src][e] == row
+                    assert not taken[row:row + counts[src, e]].any()
+                    taken[row:row + counts[src, e]] = True
+                    row += counts[src, e]
+                assert row == ends[l]
+                prev_end = ends[l]
+            assert taken.sum() == totals[1]
+    topk_idx = torch.stack([torch.randperm(8)[:2] for _ in range(50)])
+    plan = ExpertParallel(8, 2, TorchRowOps()).plan(topk_idx)
+    counts = np.bincount(topk_idx.reshape(-1).numpy(), minlength=8)[None, :]
+    _, ends, totals = peer_layout(counts, 0)
+    assert totals[0] == plan.m_pad and totals[1] == plan.n_recv
+    m_idx = plan.m_indices.numpy()
+    for e in range(8):
+        assert (m_idx == e).sum() == counts[0, e] and (counts[0, e] == 0 or np.nonzero(m_idx == e)[0].max() + 1 == ends[e])

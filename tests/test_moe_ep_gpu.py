@@ -7,7 +7,7 @@ import torch
 import deepgemm_rust_b200 as dg
 from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel, PipelinedPeerMoe
 from oracle import oracle as O
-from tests.helpers import dev, fp8_operand_1d, fp8_operand_2d, to_f32
+from tests.helpers import dev, fp8_operand_1d, fp8_operand_2d, peer_layout, to_f32
 
 pytestmark = pytest.mark.gpu
 
@@ -242,3 +242,52 @@ def test_pipelined_micro_batches_equal_the_single_batch(ctx):
             assert pipe.routed_rows() == tokens * topk
     finally:
         pipe.close()
+
+
+def test_layout_kernel_for_every_rank_of_a_larger_job(ctx):
+    # the layout kernel only sees the all-gathered count matrix, so one GPU can check what each rank of a 4-rank (and an
+    # 8-rank) job would derive, against the numpy restatement; counts include empty experts and groups that need padding
+    rng = np.random.default_rng(17)
+    for world, experts in [(4, 32), (8, 256), (1, 8)]:
+        counts = rng.integers(0, 700, (world, experts)).astype(np.uint32)
+        counts[:, 3] = 0
+        counts[world - 1, :] = rng.integers(0, 3, experts)
+        local = experts // world
+        for rank in range(world):
+            pair_base = torch.zeros(experts, dtype=torch.int32, device="cuda")
+            ends = torch.zeros(local, dtype=torch.int32, device="cuda")
+            totals = torch.zeros(4, dtype=torch.int32, device="cuda")
+            dg.ep_layout_dev(ctx, dev(counts), world, rank, experts, 128, 1 << 30, pair_base, ends, totals)
+            ctx.sync()
+            want_base, want_ends, want_totals = peer_layout(counts, rank)
+            assert np.array_equal(pair_base.cpu().numpy().view(np.uint32), want_base)
+            assert np.array_equal(ends.cpu().numpy().view(np.uint32), want_ends)
+            got = totals.cpu().numpy()
+            assert [int(got[0]), int(got[1]), int(got[3])] == want_totals and got[2] == 0
+        # a capacity one row short of the largest arena raises the overflow flag on every rank
+        dg.ep_layout_dev(ctx, dev(counts), world, 0, experts, 128, want_totals[2] - 1, pair_base, ends, totals)
+        ctx.sync()
+        assert totals.cpu().numpy()[2] == 1
+
+
+def test_pair_ranking_is_a_stable_counting_sort(ctx):
+    rng = np.random.default_rng(23)
+    experts, pairs = 40, 5000                                  # twenty chunks of 256 pairs, the last one ragged
+    ids = rng.integers(-1, experts + 1, pairs).astype(np.int32)     # -1 and `experts` are out of range: dropped
+    local_rank = torch.zeros(pairs, dtype=torch.int32, device="cuda")
+    hist = torch.zeros(dg.ep_block_hist_words(pairs, experts), dtype=torch.int32, device="cuda")
+    counts = torch.zeros(experts, dtype=torch.int32, device="cuda")
+    dg.ep_count_dev(ctx, dev(ids), pairs, experts, local_rank, hist, counts)
+    ctx.sync()
+    ok = (ids >= 0) & (ids < experts)
+    assert np.array_equal(counts.cpu().numpy(), np.bincount(ids[ok], minlength=experts))
+    # position of every kept pair among the pairs of its expert = chunk base + rank inside the chunk, in pair order
+    base = hist.cpu().numpy().reshape(-1, experts)
+    lr = local_rank.cpu().numpy()
+    seen = np.zeros(experts, np.int64)
+    for p in range(pairs):
+        if ok[p]:
+            assert base[p // 256, ids[p]] + lr[p] == seen[ids[p]]
+            seen[ids[p]] += 1
+        else:
+            assert lr[p] == -1
