@@ -1032,7 +1032,7 @@ int dg_ep_count(dg_ctx* ctx, const int32_t* expert_of_pair, uint32_t pairs, uint
     if (chunks > 0)
         dg::dg_ep_rank_pairs_kernel<<<chunks, dg::kEpChunk, num_experts * sizeof(uint32_t), ctx->stream>>>(expert_of_pair, pairs, num_experts,
                                                                                                          local_rank, block_hist);
-    dg::dg_ep_block_scan_kernel<<<ceil_div(num_experts, 256), 256, 0, ctx->stream>>>(block_hist, chunks, num_experts, counts);
+    dg::dg_ep_block_scan_kernel<<<ceil_div(num_experts, 8), 256, 0, ctx->stream>>>(block_hist, chunks, num_experts, counts);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }
@@ -1090,6 +1090,7 @@ int dg_ep_combine(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* pos
     p.tokens = tokens; p.topk = topk; p.n = n; p.experts_per_rank = num_experts / world;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     const uint64_t threads = static_cast<uint64_t>(tokens) * (n / 8);
+    if (threads > 0xFFFFFF00ull) return fail(DG_ERR_SHAPE, "tokens x n / 8 must fit 32 bits");
     uint32_t blocks = static_cast<uint32_t>((threads + 255) / 256);
     if (max_blocks != 0 && blocks > max_blocks) blocks = max_blocks;
     dg::dg_ep_combine_kernel<<<blocks, 256, 0, ctx->stream>>>(p);

@@ -131,19 +131,29 @@ __global__ void __launch_bounds__(kEpChunk) dg_ep_rank_pairs_kernel(const int32_
     for (uint32_t i = tid; i < num_experts; i += kEpChunk) block_hist[static_cast<size_t>(blockIdx.x) * num_experts + i] = ep_hist[i];
 }
 
-// Exclusive scan over chunks, per expert, in place; counts[e] = this rank's pairs for expert e.
+// Exclusive scan over chunks, per expert, in place; counts[e] = this rank's pairs for expert e.  One warp per expert:
+// 32 chunks per round (independent loads, shuffle scan), so a scan over hundreds of chunks costs a handful of memory
+// round trips instead of one per chunk.
 __global__ void __launch_bounds__(256) dg_ep_block_scan_kernel(uint32_t* __restrict__ block_hist, uint32_t num_blocks, uint32_t num_experts,
                                                                uint32_t* __restrict__ counts) {
-    const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t lane = threadIdx.x % 32;
+    const uint32_t e = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (e >= num_experts) return;
     uint32_t running = 0;
-    for (uint32_t b = 0; b < num_blocks; ++b) {
+    for (uint32_t b0 = 0; b0 < num_blocks; b0 += 32) {
+        const uint32_t b = b0 + lane;
         const size_t at = static_cast<size_t>(b) * num_experts + e;
-        const uint32_t v = block_hist[at];
-        block_hist[at] = running;
-        running += v;
+        const uint32_t v = b < num_blocks ? block_hist[at] : 0u;
+        uint32_t inc = v;                                     // inclusive scan over the 32 lanes
+        #pragma unroll
+        for (uint32_t d = 1; d < 32; d *= 2) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+            if (lane >= d) inc += up;
+        }
+        if (b < num_blocks) block_hist[at] = running + inc - v;
+        running += __shfl_sync(0xFFFFFFFFu, inc, 31);
     }
-    counts[e] = running;
+    if (lane == 0) counts[e] = running;
 }
 
 // all_counts: (world, num_experts) pairs per source rank and expert.  One block.
@@ -256,9 +266,10 @@ struct EpCombineParams {
 // chain as dg_moe_combine_kernel, reading each term from the rank that computed it.  One thread owns 8 columns.
 __global__ void __launch_bounds__(256) dg_ep_combine_kernel(const EpCombineParams p) {
     const uint32_t chunks = p.n / 8;
-    const uint64_t total = static_cast<uint64_t>(p.tokens) * chunks, stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const uint32_t t = static_cast<uint32_t>(i / chunks), c = static_cast<uint32_t>(i % chunks);
+    // tokens x chunks fits 32 bits (checked by the host): 32-bit division instead of the 64-bit sequence
+    const uint32_t total = p.tokens * chunks, stride = gridDim.x * blockDim.x;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const uint32_t t = i / chunks, c = i - t * chunks;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (uint32_t j0 = 0; j0 < p.topk; j0 += 4) {
         // up to four independent peer loads in flight before the first use
