@@ -38,26 +38,36 @@ DG_DEVICE uint32_t sf_exp_e2m1(float amax, int rule) {
 //   exp(-g) = (exp(r)) * 2^n by adding n to the exponent field;
 //   1 / (1 + exp(-g)) by three Newton steps x <- x (2 - d x) from the exponent-flip estimate 0x7EF311C7 - bits(d)
 //   (relative error 0.12 -> 4e-8; no special-function unit, no branches); silu = g * that; gates below -87 give 0.
-DG_DEVICE float silu_mul_bf16(float g, float u) {
-    const float gc = fminf(fmaxf(g, -87.0f), 30.0f);
-    const float t = __fmaf_rn(gc, -1.44269504f, 12582912.0f);
-    const float n = __fadd_rn(t, -12582912.0f);
-    float r = __fmaf_rn(n, -0.693145752f, -gc);
-    r = __fmaf_rn(n, -1.42860677e-6f, r);
-    float q = __fmaf_rn(1.0f / 120.0f, r, 1.0f / 24.0f);
-    q = __fmaf_rn(q, r, 1.0f / 6.0f);
-    q = __fmaf_rn(q, r, 0.5f);
-    q = __fmaf_rn(q, __fmul_rn(r, r), r);
-    const float s = __fadd_rn(q, 1.0f);
-    const float e = __uint_as_float(__float_as_uint(s) + (__float_as_uint(t) << 23));
-    const float d = __fadd_rn(1.0f, e);
-    float x = __uint_as_float(0x7EF311C7u - __float_as_uint(d));
-    x = __fmul_rn(x, __fmaf_rn(-d, x, 2.0f));
-    x = __fmul_rn(x, __fmaf_rn(-d, x, 2.0f));
-    x = __fmul_rn(x, __fmaf_rn(-d, x, 2.0f));
-    const float silu = g < -87.0f ? 0.0f : __fmul_rn(g, x);   // |g exp(g)| < 2e-36 below -87
-    const float act = __fmul_rn(silu, u);
-    return __uint_as_float(pack_bf16x2(0.0f, act) & 0xFFFF0000u);
+// Two elements at a time: the f32 arithmetic goes through the packed f32x2 instructions of sm_100 (two IEEE
+// operations per instruction, same results as the scalar forms), halving the arithmetic instruction count.
+DG_DEVICE float2 silu_mul_bf16x2(float2 g, float2 u) {
+    const float2 gc = make_float2(fminf(fmaxf(g.x, -87.0f), 30.0f), fminf(fmaxf(g.y, -87.0f), 30.0f));
+    const float2 magic = make_float2(12582912.0f, 12582912.0f);
+    const float2 t = __ffma2_rn(gc, make_float2(-1.44269504f, -1.44269504f), magic);
+    const float2 n = __fadd2_rn(t, make_float2(-12582912.0f, -12582912.0f));
+    const float2 ngc = make_float2(-gc.x, -gc.y);
+    float2 r = __ffma2_rn(n, make_float2(-0.693145752f, -0.693145752f), ngc);
+    r = __ffma2_rn(n, make_float2(-1.42860677e-6f, -1.42860677e-6f), r);
+    float2 q = __ffma2_rn(make_float2(1.0f / 120.0f, 1.0f / 120.0f), r, make_float2(1.0f / 24.0f, 1.0f / 24.0f));
+    q = __ffma2_rn(q, r, make_float2(1.0f / 6.0f, 1.0f / 6.0f));
+    q = __ffma2_rn(q, r, make_float2(0.5f, 0.5f));
+    q = __ffma2_rn(q, __fmul2_rn(r, r), r);
+    const float2 one = make_float2(1.0f, 1.0f), two = make_float2(2.0f, 2.0f);
+    const float2 s = __fadd2_rn(q, one);
+    const float2 e = make_float2(__uint_as_float(__float_as_uint(s.x) + (__float_as_uint(t.x) << 23)),
+                                 __uint_as_float(__float_as_uint(s.y) + (__float_as_uint(t.y) << 23)));
+    const float2 d = __fadd2_rn(one, e);
+    const float2 nd = make_float2(-d.x, -d.y);
+    float2 x = make_float2(__uint_as_float(0x7EF311C7u - __float_as_uint(d.x)), __uint_as_float(0x7EF311C7u - __float_as_uint(d.y)));
+    x = __fmul2_rn(x, __ffma2_rn(nd, x, two));
+    x = __fmul2_rn(x, __ffma2_rn(nd, x, two));
+    x = __fmul2_rn(x, __ffma2_rn(nd, x, two));
+    float2 silu = __fmul2_rn(g, x);
+    silu.x = g.x < -87.0f ? 0.0f : silu.x;   // |g exp(g)| < 2e-36 below -87
+    silu.y = g.y < -87.0f ? 0.0f : silu.y;
+    const float2 act = __fmul2_rn(silu, u);
+    const uint32_t packed = pack_bf16x2(act.x, act.y);
+    return make_float2(__uint_as_float(packed << 16), __uint_as_float(packed & 0xFFFF0000u));
 }
 
 struct CastParams {
@@ -107,7 +117,11 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
             const float u[8] = {bf16_lo(raw_up[h].x), bf16_hi(raw_up[h].x), bf16_lo(raw_up[h].y), bf16_hi(raw_up[h].y),
                                 bf16_lo(raw_up[h].z), bf16_hi(raw_up[h].z), bf16_lo(raw_up[h].w), bf16_hi(raw_up[h].w)};
             #pragma unroll
-            for (uint32_t i = 0; i < 8; ++i) v[i] = silu_mul_bf16(v[i], u[i]);
+            for (uint32_t i = 0; i < 8; i += 2) {
+                const float2 a = silu_mul_bf16x2(make_float2(v[i], v[i + 1]), make_float2(u[i], u[i + 1]));
+                v[i] = a.x;
+                v[i + 1] = a.y;
+            }
         }
         float amax = 0.0f;
         #pragma unroll
