@@ -209,9 +209,9 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
     for (uint32_t ctas = 1; ctas <= 2; ++ctas) {
         if (force_ctas && static_cast<uint32_t>(atoi(force_ctas)) != ctas) continue;
         const uint32_t tile_m = 128 * ctas;
-        // contiguous layout: a 256-row pair tile may run past its group's end; the rows beyond it are computed but
-        // never stored (groups start on multiples of 128, stores are 32 rows tall), so any 128-multiple alignment works
-        if (ctas == 2 && d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS && align % 128 != 0) continue;
+        // contiguous layout: a tile may run past its group's end into the next groups' rows; those rows are computed but
+        // never stored (stores are 32 rows tall and stop at the group end; an alignment of 16 switches the last box of a
+        // group to row-exact stores), so every alignment from 16 to 256 works with 128- and 256-row tiles
         if (ctas == 2 && sms < 2) continue;
         // expected row-tiles.  Grouped layouts: a group of r valid rows needs ceil(r / tile_m) tiles, on average
         // r / tile_m + 1/2 when group sizes are spread out; the contiguous arena's m includes about half an alignment of
@@ -433,8 +433,6 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         if (out->sfd_len < static_cast<size_t>(pr.n / 128) * a_groups * align4(pr.m)) return fail(DG_ERR_SHAPE, "sfd buffer too small");
     }
     const uint32_t align = g_mk_alignment.load();
-    if (contiguous && align % 128 != 0)
-        return fail(DG_ERR_UNSUPPORTED, "contiguous layout: mk alignment %u is not a multiple of the 128-row tile", align);
 
     dg_desc desc = {pr.type, pr.m, pr.n, pr.k, pr.groups, pr.expected_m, a->bits, b->bits, a->gran_k, b->gran_k,
                     static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms)};
@@ -543,6 +541,11 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.sf_a_cols = sfa_cols;
     p.sf_b_cols = sfb_cols;
     p.mk_alignment = align;
+    // groups start at multiples of `align` rows; tiles stay 128 (or 256) rows tall and simply run into the next group's rows,
+    // which are computed and not stored.  Stores go out in 32-row boxes, so only an alignment of 16 needs row-exact stores.
+    p.mask_rows = (contiguous && align % 32 != 0) ? 1 : 0;
+    p.out_ptr = out->buf;
+    p.out_ld = out->ld;
     p.accumulate = e.accumulate ? 1 : 0;
     p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges alpha is applied to the sum
     p.alpha = e.alpha;

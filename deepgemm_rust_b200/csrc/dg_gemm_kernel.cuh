@@ -56,6 +56,10 @@ struct GemmParams {
     uint32_t kb_per_split;     // k-blocks per range (a multiple of every scale-word period)
     uint32_t mk_alignment;     // contiguous layout: every group starts at a multiple of this
     uint32_t has_alpha;
+    uint32_t mask_rows;        // contiguous layout whose groups start at multiples of 16 rows: a 32-row store box can reach
+                               // into the next group, so boxes that cross the group end are written row by row instead
+    void* out_ptr;             // output base and leading dimension (elements), used by those row-by-row stores only
+    uint32_t out_ld;
     uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
     float alpha;
     uint32_t sfd_stride;       // output scale words: stride between word columns (fp8 output)
@@ -560,6 +564,26 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                             w[q] = cvt_e4m3x4(scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 0]), inv), scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 1]), inv),
                                               scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 2]), inv), scale_pos_zero(__uint_as_float(v[16 * j + 4 * q + 3]), inv));
                         st_shared_v4(row_addr + chunk * 16, w[0], w[1], w[2], w[3]);
+                    }
+                }
+                if constexpr (kOut != kOutFp8) {
+                    if (p.mask_rows && row0 < t.m_end && row0 + 32 > t.m_end) {
+                        // this box crosses the end of the group: each lane writes its own row's 32 columns, if the row is valid
+                        const uint32_t col0 = t.n0 + s * 32;
+                        if (row < t.m_end) {
+                            constexpr uint32_t kElem = kOut == kOutBf16 ? 2 : 4;
+                            uint8_t* dst = static_cast<uint8_t*>(p.out_ptr) + (static_cast<size_t>(row) * p.out_ld + col0) * kElem;
+                            #pragma unroll
+                            for (uint32_t i = 0; i < 32; ++i) {
+                                if (col0 + i < p.n) {
+                                    if constexpr (kOut == kOutBf16)
+                                        reinterpret_cast<uint16_t*>(dst)[i] = static_cast<uint16_t>(pack_bf16x2(__uint_as_float(v[i]), 0.0f) & 0xFFFFu);
+                                    else
+                                        reinterpret_cast<uint32_t*>(dst)[i] = v[i];
+                                }
+                            }
+                        }
+                        return;
                     }
                 }
                 if (sub_in_buf + 1 == kSubsPerBuf) {

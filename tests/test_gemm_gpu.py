@@ -253,6 +253,48 @@ def test_m_grouped_contiguous(ctx, sizes, n, k, ctas, monkeypatch):
 
 
 @pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("out_kind", [0, 1])
+@pytest.mark.parametrize("alignment", [64, 32, 16, 256])
+def test_m_grouped_contiguous_other_alignments(ctx, alignment, out_kind, ctas, monkeypatch):
+    # set_mk_alignment_for_contiguous_layout (types.rs:195): groups start at multiples of 16..256 rows.  Tiles stay 128 / 256
+    # rows tall, so a group's last tile runs into the following groups' rows: those must come out as their own group computes
+    # them, never as this tile computes them (several rounds: a wrong store would race with the right one)
+    monkeypatch.setenv("DG_CTAS", str(ctas))
+    sizes, n, k = [37, 5, 0, 130, 64, 1, 17, 200, 16, 3], 328, 640
+    groups = len(sizes)
+    m_idx, starts = contiguous_layout(sizes, alignment)
+    m_total = len(m_idx)
+    _, aq, asf = fp8_operand_1d(m_total, k, 61)
+    _, bq, bsf = fp8_operand_1d(groups * n, k, 62, 128, groups)       # per-row scales: n need not be a multiple of 128
+    valid = np.nonzero(m_idx >= 0)[0]
+    want = np.zeros((m_total, n), np.float32)
+    for g in range(groups):
+        rows = valid[m_idx[valid] == g].astype(np.uint32)
+        if rows.size:
+            want[rows.astype(np.int64)] = O.lp_gemm_rows(aq, asf, 8, 128, 1, m_total, rows, bq, bsf, 8, 128, groups, n,
+                                                         np.arange(g * n, (g + 1) * n, dtype=np.uint32), k)
+    ld = 336
+    dg.set_mk_alignment_for_contiguous_layout(alignment)
+    try:
+        assert dg.get_mk_alignment_for_contiguous_layout() == alignment
+        for _ in range(4):
+            d = torch.full((m_total, ld), float("nan"), dtype=torch.bfloat16 if out_kind == 0 else torch.float32, device="cuda")
+            dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, lp(aq, asf, m_total, k), dev(m_idx), lp(bq, bsf, groups * n, k),
+                                                     dg.Sm100Out(out_kind, d, ld), groups)
+            ctx.sync()
+            dn = to_f32(d)
+            assert not np.isnan(dn[valid][:, :n]).any()
+            assert np.isnan(dn[:, n:]).all()                      # columns past n are never written
+            diff = O.calc_diff(dn[valid][:, :n], want[valid])
+            assert diff <= (TIGHT_BF16 if out_kind == 0 else TIGHT_F32), diff
+            # row-wise: a row taken from the wrong group would show up as a large per-row error
+            err = np.abs(dn[valid][:, :n] - want[valid]).max(axis=1)
+            assert (err <= 0.02 * np.abs(want[valid]).max()).all()
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+
+
+@pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("masked,m_max,n,k", [
     ([37, 128, 1, 64, 15, 100, 128, 3], 128, 256, 512),   # reference fixture (tests/e2e.rs:131,566)
     ([0, 256, 17, 129, 255, 16, 0, 1], 256, 384, 1024),
@@ -445,11 +487,8 @@ def test_argument_errors(ctx):
     assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, bad, b, out)) == "Shape"                               # k mismatch
     assert kind(lambda: dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.Bf16(d, 64))) == "Shape"             # ld < n
     assert kind(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, dev(np.zeros(128, np.int32)), b, out, 3)) == "Shape"
-    dg.set_mk_alignment_for_contiguous_layout(64)
-    try:
-        assert kind(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, dev(np.zeros(128, np.int32)), b, out, 1)) == "Unsupported"
-    finally:
-        dg.set_mk_alignment_for_contiguous_layout(128)
+    with pytest.raises(dg.DgError):
+        dg.set_mk_alignment_for_contiguous_layout(48)          # not a power of two (types.rs:196)
     ctx.sync()
 
 
