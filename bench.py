@@ -274,7 +274,7 @@ class DenseWork:
 class MoeWork:
     """Expert-parallel contiguous grouped GEMM pair (see the module docstring)."""
 
-    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer", chunks=1, blocks_per_sm=2):
+    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer", chunks=1, blocks_per_sm=2, fused_act=True):
         from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel, PipelinedPeerMoe
         self.torch, self.dg, self.ctx, self.dev, self.world = torch, dg, ctx, dev, world
         c = self.c = dict(MOE)
@@ -304,6 +304,7 @@ class MoeWork:
         del x
         # rows travel through peer memory (kernels of the library) unless the peers cannot be mapped; every rank must agree
         self.peer, self.pipe, self.chunks, self.exchange_note = None, None, max(1, chunks), "nccl all_to_all_single"
+        self.fused_act = False
         if exchange == "peer":
             try:
                 if self.chunks > 1:
@@ -327,9 +328,12 @@ class MoeWork:
             self.exchange_note = "peer-memory stores/loads (library kernels) + count all-gather" if world > 1 else "none (local arena)"
             if self.pipe is not None:
                 self.exchange_note += f"; {self.chunks} token micro-batches, exchange of one overlapping the GEMMs of another"
-            # per micro-batch: gate/up output and the quantised activation (capacity rows each)
-            self.bufs = {id(pe): (torch.empty((cap, c["gate_up_n"]), dtype=torch.bfloat16, device=dev),
-                                  (torch.empty((cap, c["down_k"]), dtype=torch.uint8, device=dev), dg.alloc_sf(ctx, cap, c["down_k"], 128)))
+            # per micro-batch: gate/up output (only when the activation is a kernel of its own) and the quantised activation
+            # (capacity rows each); the fused epilogue writes one scale per 32 columns, the separate kernel one per 128
+            self.fused_act = fused_act
+            self.act_gran = 32 if fused_act else 128
+            self.bufs = {id(pe): (None if fused_act else torch.empty((cap, c["gate_up_n"]), dtype=torch.bfloat16, device=dev),
+                                  (torch.empty((cap, c["down_k"]), dtype=torch.uint8, device=dev), dg.alloc_sf(ctx, cap, c["down_k"], self.act_gran)))
                          for pe in (self.pipe.exchanges if self.pipe is not None else [self.peer])}
             self.h, self.act = self.bufs[id(self.peer)]
         else:
@@ -339,8 +343,8 @@ class MoeWork:
         self.flops_per_row = 2.0 * (c["gate_up_n"] * c["hidden"] + c["down_n"] * c["down_k"])
         self.rows = 0
         if self.peer is not None:
-            # per micro-batch: pair ranking, chunk scan, layout, dispatch, 2 GEMMs, SiLU-mul quantiser, combine
-            self.launches = 8 * self.chunks
+            # per micro-batch: pair ranking, chunk scan, layout, dispatch, 2 GEMMs, combine (+ the SiLU-mul quantiser when not fused)
+            self.launches = (7 if self.fused_act else 8) * self.chunks
         else:
             # pack, unpack, 2 x (group-end kernel, scan kernel, GEMM), SiLU-mul quantiser, combine, plus the result gather when rows travel
             self.launches = 10 + (1 if world > 1 else 0)
@@ -378,10 +382,14 @@ class MoeWork:
         down grouped GEMM into the buffer the combine reads."""
         dg, c, ctx = self.dg, self.c, self.ctx
         h, act = self.bufs[id(pe)]
-        dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(h, c["gate_up_n"]), self.local_e)
-        dg.silu_mul_cast_fp8_sf_dev(ctx, h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=act)
-        dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, dg.LpOperand(act[0], act[1], pe.capacity, c["down_k"], c["down_k"]), ends,
-                                                      self.w2, dg.Sm100Out.Bf16(pe.result, c["down_n"]), self.local_e)
+        if self.fused_act:
+            # the weights are [gate rows; up rows] per expert: the epilogue writes e4m3(silu(gate) * up) and its scales
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, self.w1, dg.Sm100Out.SwiGluFp8(act[0], c["down_k"], act[1]), self.local_e)
+        else:
+            dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(h, c["gate_up_n"]), self.local_e)
+            dg.silu_mul_cast_fp8_sf_dev(ctx, h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=act)
+        dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, dg.LpOperand(act[0], act[1], pe.capacity, c["down_k"], c["down_k"], 8, self.act_gran),
+                                                      ends, self.w2, dg.Sm100Out.Bf16(pe.result, c["down_n"]), self.local_e)
 
     def routed_rows(self):
         """Valid arena rows of this rank in the last step (a host read, outside any timed region)."""
@@ -434,7 +442,8 @@ class MoeWork:
             for _ in range(6):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(self.ctx, a_op, ends, self.w1, dg.Sm100Out.Bf16(self.h, c["gate_up_n"]), self.local_e)
+                out = dg.Sm100Out.SwiGluFp8(self.act[0], c["down_k"], self.act[1]) if self.fused_act else dg.Sm100Out.Bf16(self.h, c["gate_up_n"])
+                dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(self.ctx, a_op, ends, self.w1, out, self.local_e)
                 e1.record()
                 torch.cuda.synchronize()
                 times.append(e0.elapsed_time(e1))
@@ -548,7 +557,7 @@ def run_config_table(args, torch, dg, ctx, dev, peaks):
     for experts in (MOE["experts"], MOE["experts"] // 8):
         saved = dict(MOE)
         MOE["experts"] = experts
-        moe = MoeWork(torch, None, dg, ctx, dev, 0, 1, "peer")
+        moe = MoeWork(torch, None, dg, ctx, dev, 0, 1, "peer", fused_act=False)
         MOE.update(saved)
         pe, c = moe.peer, moe.c
         a_op, ends = pe.dispatch(moe.topi, moe.xq, moe.xsf)
@@ -561,6 +570,10 @@ def run_config_table(args, torch, dg, ctx, dev, peaks):
         add(f"grouped gate/up ({tag})", t, 2.0 * rows_valid * n * k, rows_valid * k + experts * n * k + 2 * rows_valid * n + sf_bytes(k, 128, rows_valid + experts * n), tc8)
         t = timeit(lambda: dg.silu_mul_cast_fp8_sf_dev(ctx, moe.h, c["gate_up_n"], pe.capacity, c["down_k"], 128, live_rows=pe.totals, out=moe.act))
         add(f"silu*up + quantise ({tag})", t, 0.0, rows_valid * c["down_k"] * 5, tc8)
+        act32 = (moe.act[0], dg.alloc_sf(ctx, pe.capacity, c["down_k"], 32))
+        t = timeit(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, a_op, ends, moe.w1, dg.Sm100Out.SwiGluFp8(act32[0], c["down_k"], act32[1]), experts))
+        add(f"grouped gate/up with silu*up + quantise in its epilogue ({tag})", t, 2.0 * rows_valid * n * k,
+            rows_valid * k + experts * n * k + rows_valid * c["down_k"] * (1 + 1 / 32) + sf_bytes(k, 128, rows_valid + experts * n), tc8)
         n, k = c["down_n"], c["down_k"]
         t = timeit(lambda: dg.m_grouped_fp8_fp4_gemm_contiguous_ends_dev(ctx, act_op, ends, moe.w2, y_out, experts))
         add(f"grouped down ({tag})", t, 2.0 * rows_valid * n * k, rows_valid * k + experts * n * k + 2 * rows_valid * n + sf_bytes(k, 128, rows_valid + experts * n), tc8)
@@ -589,6 +602,8 @@ def main():
                     help="token micro-batches of the MoE step whose exchange overlaps the other micro-batches' GEMMs (measured slower "
                          "than 1 on 2 and 4 GPUs: the GEMMs lose more to the exchange kernels sharing their SMs than the overlap returns)")
     ap.add_argument("--ep-blocks-per-sm", type=int, default=2, help="grid bound of the exchange kernels when they run beside the GEMMs")
+    ap.add_argument("--unfused-act", action="store_true",
+                    help="MoE step: gate/up GEMM writes bf16 and a separate kernel applies silu(gate)*up and quantises (default: fused into the GEMM's epilogue)")
     ap.add_argument("--moe-tokens", type=int, default=None, help="moe_ep: tokens per rank (default 8192); smaller values for profiling captures")
     ap.add_argument("--only", default=None, help="M,N,K: run just this dense GEMM (profiling captures); implies --workload dense_fp8")
     args = ap.parse_args()
@@ -629,7 +644,7 @@ def main():
     # ---- build the workload (untimed): operands resident in HBM, quantised by the library's own kernels
     dense = DenseWork(torch, dg, ctx, dev, 1000 + rank) if args.workload in ("dsv3", "dense_fp8") else None
     chunks = max(1, args.moe_chunks)
-    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep, chunks, args.ep_blocks_per_sm) if args.workload in ("dsv3", "moe_ep") else None
+    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep, chunks, args.ep_blocks_per_sm, not args.unfused_act) if args.workload in ("dsv3", "moe_ep") else None
     ctx.sync()
 
     def step(record=None):

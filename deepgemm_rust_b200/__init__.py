@@ -214,7 +214,8 @@ class LpOperand:
 
 @dataclass
 class Sm100Out:
-    """ops_sm100.rs:95-110.  kind 0 = bf16, 1 = f32, 2 = e4m3 with per-row per-32-column UE8M0 scales."""
+    """ops_sm100.rs:95-110.  kind 0 = bf16, 1 = f32, 2 = e4m3 with per-row per-32-column UE8M0 scales,
+    3 = the same for silu(gate) * up of a gate|up weight block (fused activation)."""
     kind: int
     buf: torch.Tensor
     ld: int
@@ -231,6 +232,12 @@ class Sm100Out:
     @classmethod
     def Fp8(cls, buf, ld, sfd):
         return cls(2, buf, ld, sfd)
+
+    @classmethod
+    def SwiGluFp8(cls, buf, ld, sfd):
+        """b holds n gate rows then n up rows per group; buf (rows, ld) receives e4m3(silu(gate) * up), sfd its per-32-column
+        UE8M0 scale words: together the next GEMM's A operand with gran_k = 32."""
+        return cls(3, buf, ld, sfd)
 
     def _c(self) -> _Out:
         return _Out(self.kind, self.buf.data_ptr(), self.ld, self.sfd.data_ptr() if self.sfd is not None else None,

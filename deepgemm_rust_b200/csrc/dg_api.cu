@@ -190,7 +190,9 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
     const uint32_t half_k = mxf4 ? 256 : 128;     // K elements of one 128-byte slab
     const uint32_t sms = d->num_sms ? d->num_sms : 148;
     const uint32_t groups = d->num_groups ? d->num_groups : 1;
-    const uint32_t step = d->cd_dtype == DG_OUT_FP8 ? 128 : 32;
+    // the fused gate/up activation writes block_n / 2 columns per tile in 32-column scale blocks: widths of 64
+    const bool swiglu = d->cd_dtype == DG_OUT_SWIGLU_FP8;
+    const uint32_t step = d->cd_dtype == DG_OUT_FP8 ? 128 : (swiglu ? 64 : 32);
     const uint32_t align = g_mk_alignment.load();
     const char* force_n = getenv("DG_BLOCK_N");
     const char* force_ctas = getenv("DG_CTAS");
@@ -213,6 +215,7 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
         // never stored (stores are 32 rows tall and stop at the group end; an alignment of 16 switches the last box of a
         // group to row-exact stores), so every alignment from 16 to 256 works with 128- and 256-row tiles
         if (ctas == 2 && sms < 2) continue;
+        if (swiglu && ctas != 2) continue;        // gate rows on one CTA of the pair, up rows on the other
         // expected row-tiles.  Grouped layouts: a group of r valid rows needs ceil(r / tile_m) tiles, on average
         // r / tile_m + 1/2 when group sizes are spread out; the contiguous arena's m includes about half an alignment of
         // padding per group.
@@ -234,6 +237,7 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
             const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
             if (bn + sf_cols > 512) continue;
             const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
+            if (swiglu && accum == 1 && !force_n) continue;   // its epilogue is long: only worth it behind a second accumulator
             const uint32_t tiles = static_cast<uint32_t>(m_blocks * ceil_div(d->n, bn) + 0.999);
             // cycles per tile, fitted to measurements on B200 (dense 4096x7168x4096, every width, 1 and 2 CTAs):
             // per k-block max(UMMA time, load time) + ~150 of issue-side overhead, where one UMMA (K = 32 bytes) takes
@@ -242,11 +246,11 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
             const uint32_t total_kb = ceil_div(d->k, block_k);
             const double mma = 4.0 * (bn * 0.5 > 118.0 ? bn * 0.5 : 118.0);
             const double feed = (16384.0 + bn / ctas * 128.0) / 77.0;
-            const double epilogue = accum == 1 ? 10.5 * bn : 1.0 * bn;
+            const double epilogue = swiglu ? (accum == 1 ? 40.0 * bn : 1.0 * bn) : (accum == 1 ? 10.5 * bn : 1.0 * bn);
             const double per_kb = halves * (mma > feed ? mma : feed) + 150.0;
             // K ranges (dense GEMMs with f32-summable outputs only): each range is a multiple of 4 k-blocks so scale words
             // never straddle ranges; the partial sums cost a second small kernel (launch + S reads of the M x N f32 tile set)
-            const bool may_split = d->gemm_type == DG_GEMM_NORMAL && d->cd_dtype != DG_OUT_FP8 && d->n % 4 == 0 && !no_k_ranges;
+            const bool may_split = d->gemm_type == DG_GEMM_NORMAL && d->cd_dtype != DG_OUT_FP8 && !swiglu && d->n % 4 == 0 && !no_k_ranges;
             for (uint32_t splits = 1; splits <= 16; ++splits) {
                 if (splits > 1 && (!may_split || halves > 1)) break;
                 if (force_splits && static_cast<uint32_t>(atoi(force_splits)) != splits) continue;
@@ -401,17 +405,27 @@ template <uint32_t kFmt, uint32_t kCtas>
 cudaError_t launch_by_out(int kind, const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
     if (kind == DG_OUT_BF16) return launch_kernel<kFmt, dg::kOutBf16, kCtas>(p, grid, smem, stream, maps);
     if (kind == DG_OUT_F32) return launch_kernel<kFmt, dg::kOutF32, kCtas>(p, grid, smem, stream, maps);
-    if constexpr (kFmt != dg::kFmtBf16) return launch_kernel<kFmt, dg::kOutFp8, kCtas>(p, grid, smem, stream, maps);
+    if constexpr (kFmt == dg::kFmtMxf8f6f4 && kCtas == 2)
+        if (kind == DG_OUT_SWIGLU_FP8) return launch_kernel<kFmt, dg::kOutSwiGluFp8, kCtas>(p, grid, smem, stream, maps);
+    if constexpr (kFmt != dg::kFmtBf16)
+        if (kind == DG_OUT_FP8) return launch_kernel<kFmt, dg::kOutFp8, kCtas>(p, grid, smem, stream, maps);
     return cudaErrorInvalidValue;
 }
 
 int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi, const Problem& pr) {
     if (out == nullptr || out->buf == nullptr) return fail(DG_ERR_SHAPE, "null output");
-    if (out->kind < DG_OUT_BF16 || out->kind > DG_OUT_FP8) return fail(DG_ERR_SHAPE, "invalid output kind %d", out->kind);
+    if (out->kind < DG_OUT_BF16 || out->kind > DG_OUT_SWIGLU_FP8) return fail(DG_ERR_SHAPE, "invalid output kind %d", out->kind);
     dg_epilogue e = {1.0f, 0, 0, 100};
     if (epi) e = *epi;
-    if (out->kind == DG_OUT_FP8 && (e.has_alpha || e.accumulate))
+    const bool swiglu = out->kind == DG_OUT_SWIGLU_FP8;
+    const bool fp8_out = out->kind == DG_OUT_FP8 || swiglu;
+    if (fp8_out && (e.has_alpha || e.accumulate))
         return fail(DG_ERR_SHAPE, "the FP8-quantized output cannot combine alpha/accumulation");
+    if (swiglu) {
+        if (pr.bf16 || a->bits != 8 || b->bits != 8 || b->gran_k != 128)
+            return fail(DG_ERR_UNSUPPORTED, "the fused gate/up activation takes e4m3 operands with per-128 weight scales");
+        if (pr.n % 256 != 0) return fail(DG_ERR_SHAPE, "gate|up weights: rows per group (%u) must be 2 x a multiple of 128", pr.n);
+    }
     if (e.accumulate && e.has_alpha) return fail(DG_ERR_SHAPE, "alpha and accumulation are mutually exclusive");
     if (a->k != b->k) return fail(DG_ERR_SHAPE, "a.k (%u) != b.k (%u)", a->k, b->k);
     if (pr.m == 0 || pr.n == 0) return DG_OK;
@@ -423,16 +437,19 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     rc = pr.bf16 ? DG_OK : check_operand(b, "b", pr.n * b_groups, b_groups);
     if (rc) return rc;
     const uint32_t d_rows = pr.m * a_groups;
-    const uint32_t d_elem = out->kind == DG_OUT_F32 ? 4 : (out->kind == DG_OUT_FP8 ? 1 : 2);
-    if (out->ld < pr.n) return fail(DG_ERR_SHAPE, "output ld (%u) smaller than n (%u)", out->ld, pr.n);
+    const uint32_t d_elem = out->kind == DG_OUT_F32 ? 4 : (fp8_out ? 1 : 2);
+    const uint32_t n_out = swiglu ? pr.n / 2 : pr.n;     // output columns (the fused activation halves them)
+    if (out->ld < n_out) return fail(DG_ERR_SHAPE, "output ld (%u) smaller than n (%u)", out->ld, n_out);
     if ((static_cast<size_t>(out->ld) * d_elem) % 16 != 0) return fail(DG_ERR_SHAPE, "output row pitch must be a multiple of 16 bytes");
-    if (out->buf_len < static_cast<size_t>(d_rows - 1) * out->ld + pr.n) return fail(DG_ERR_SHAPE, "output buffer too small");
-    if (out->kind == DG_OUT_FP8) {
+    if (out->buf_len < static_cast<size_t>(d_rows - 1) * out->ld + n_out) return fail(DG_ERR_SHAPE, "output buffer too small");
+    if (fp8_out) {
         if (out->sfd == nullptr) return fail(DG_ERR_SHAPE, "FP8 output needs sfd");
-        if (pr.n % 128 != 0) return fail(DG_ERR_SHAPE, "FP8 output needs n to be a multiple of 128");
-        if (out->sfd_len < static_cast<size_t>(pr.n / 128) * a_groups * align4(pr.m)) return fail(DG_ERR_SHAPE, "sfd buffer too small");
+        if (n_out % 128 != 0) return fail(DG_ERR_SHAPE, "FP8 output needs n to be a multiple of 128");
+        if (out->sfd_len < static_cast<size_t>(n_out / 128) * a_groups * align4(pr.m)) return fail(DG_ERR_SHAPE, "sfd buffer too small");
     }
     const uint32_t align = g_mk_alignment.load();
+    if (swiglu && contiguous && align % 32 != 0)
+        return fail(DG_ERR_UNSUPPORTED, "the fused gate/up activation needs an mk alignment of at least 32");
 
     dg_desc desc = {pr.type, pr.m, pr.n, pr.k, pr.groups, pr.expected_m, a->bits, b->bits, a->gran_k, b->gran_k,
                     static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms)};
@@ -492,7 +509,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         if (rc) return rc;
         uint64_t bdims[2] = {align4(pr.n), static_cast<uint64_t>(sfb_cols) * b_groups};
         uint64_t bstrides[1] = {static_cast<uint64_t>(align4(pr.n)) * 4};
-        uint32_t bbox[2] = {sf_block_n, sfb_words};
+        uint32_t bbox[2] = {swiglu ? cfg.block_n / 2 : sf_block_n, sfb_words};   // fused activation: gate rows and up rows as two boxes
         rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? b->data : b->sf, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB");
         if (rc) return rc;
     }
@@ -506,13 +523,13 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
             rc = encode_map(&maps[4], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, ctx->splitk_ws, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "D partials");
         } else {
             const CUtensorMapDataType dt = out->kind == DG_OUT_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                           : (out->kind == DG_OUT_FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+                                           : (fp8_out ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
             const uint64_t pitch = static_cast<uint64_t>(out->ld) * d_elem;
-            uint64_t dims[3] = {pr.n, pr.m, a_groups};
+            uint64_t dims[3] = {n_out, pr.m, a_groups};
             uint64_t strides[2] = {pitch, pitch * pr.m};
-            uint32_t box[3] = {out->kind == DG_OUT_FP8 ? 128u : 32u, 32, 1};
+            uint32_t box[3] = {out->kind == DG_OUT_FP8 ? 128u : 32u, 32, 1};   // the fused activation stores 32 x 32 bytes, unswizzled
             rc = encode_map(&maps[4], dt, 3, out->buf, dims, strides, box,
-                            out->kind == DG_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, "D");
+                            swiglu ? CU_TENSOR_MAP_SWIZZLE_NONE : (out->kind == DG_OUT_BF16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B), "D");
         }
         if (rc) return rc;
     }
@@ -520,8 +537,9 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     dg::GemmParams p;
     memset(&p, 0, sizeof(p));
     p.m = pr.m;
-    p.n = pr.n;
+    p.n = n_out;
     p.k = pr.k;
+    p.tile_n = swiglu ? cfg.block_n / 2 : cfg.block_n;
     p.num_groups = pr.groups;
     p.gemm_type = pr.type;
     p.block_n = cfg.block_n;

@@ -24,11 +24,15 @@
 // in 512 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
 #pragma once
 #include "dg_ptx.cuh"
+#include "dg_activation.cuh"
 
 namespace dg {
 
 enum GemmType : uint32_t { kGemmNormal = 0, kGemmContiguous = 1, kGemmMasked = 2, kGemmBatched = 3 };
-enum OutKind : uint32_t { kOutBf16 = 0, kOutF32 = 1, kOutFp8 = 2 };
+// kOutSwiGluFp8: B holds, per group, n gate rows followed by n up rows; a tile's accumulator is [gate columns | up columns] of
+// the same n-range and the epilogue writes e4m3(silu(gate) * up) with one UE8M0 scale per 32 columns (CTA pairs only:
+// rank 0 loads the gate rows of B, rank 1 the up rows).
+enum OutKind : uint32_t { kOutBf16 = 0, kOutF32 = 1, kOutFp8 = 2, kOutSwiGluFp8 = 3 };
 enum OperandFmt : uint32_t { kFmtMxf8f6f4 = 0, kFmtMxf4 = 1, kFmtBf16 = 2 };
 
 constexpr uint32_t kBlockM = 128;          // UMMA M, rows of A per tile
@@ -37,14 +41,16 @@ constexpr uint32_t kUmmaKBytes = 32;       // K bytes consumed by one UMMA
 constexpr uint32_t kMaxStages = 12;
 constexpr uint32_t kNumThreads = 256;
 // staging buffer of one epilogue warp: 32 rows x 64 bytes (bf16, 32 columns) or x 128 bytes (f32 / e4m3)
-constexpr uint32_t epilogue_buf_bytes(uint32_t out_kind) { return out_kind == 0 ? 2048u : 4096u; }
+// (the fused activation stages 32 rows x 32 bytes)
+constexpr uint32_t epilogue_buf_bytes(uint32_t out_kind) { return out_kind == 0 ? 2048u : (out_kind == 3 ? 1024u : 4096u); }
 constexpr uint32_t kTmemCols = 512;
 
 struct GemmParams {
-    uint32_t m, n, k;          // m: rows per group (contiguous: rows of the whole arena)
+    uint32_t m, n, k;          // m: rows per group (contiguous: rows of the whole arena); n: output columns
     uint32_t num_groups;
     uint32_t gemm_type;
-    uint32_t block_n;
+    uint32_t block_n;          // UMMA N = accumulator columns of a tile
+    uint32_t tile_n;           // output columns of a tile: block_n, or block_n / 2 for the fused gate/up activation
     uint32_t block_k_elems;    // 128 (e4m3) or 256 (packed e2m1)
     uint32_t num_stages;
     uint32_t num_accum_stages;
@@ -100,7 +106,7 @@ struct Scheduler {
         worker = blockIdx.x / ctas;
         num_workers = gridDim.x / ctas;
         num_m_blocks = (p.m + tile_m - 1) / tile_m;
-        num_n_blocks = (p.n + p.block_n - 1) / p.block_n;
+        num_n_blocks = (p.n + p.tile_n - 1) / p.tile_n;
         iter = 0;
         cur_group = 0;
         cum_begin = 0;
@@ -158,7 +164,7 @@ struct Scheduler {
             const uint32_t nb = in_band / rows_here, mb = first_m + (in_band - nb * rows_here);
             t.m0 = mb * tile_m;
             t.m_end = p.m;
-            t.n0 = nb * p.block_n;
+            t.n0 = nb * p.tile_n;
             t.ga = t.gb = g;
             t.gd = p.num_splits > 1 ? split : g;
             return true;
@@ -175,7 +181,7 @@ struct Scheduler {
         const uint32_t nb = in_group / cur_m_blocks, ml = in_group - nb * cur_m_blocks;
         t.m0 = cur_row_start + ml * tile_m;
         t.m_end = cur_row_end;
-        t.n0 = nb * p.block_n;
+        t.n0 = nb * p.tile_n;
         t.gb = cur_group;
         t.ga = p.gemm_type == kGemmContiguous ? 0u : cur_group;
         t.gd = t.ga;
@@ -289,7 +295,9 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         const uint32_t full_bar_leader = kCtas == 2 ? mapa_u32(smem_u32(bar_full), 0) : 0u;
         while (ok && sched.next(t)) {
             const int32_t row_a = static_cast<int32_t>(t.m0 + cta_rank * kBlockM);
-            const int32_t row_b = static_cast<int32_t>(t.n0 + cta_rank * load_n);
+            // fused gate/up activation: rank 0 takes the gate rows [n0, n0 + load_n) of the group's B block, rank 1 the up rows
+            // of the same range, which start p.n rows further down
+            const int32_t row_b = static_cast<int32_t>(kOut == kOutSwiGluFp8 ? t.n0 + cta_rank * p.n : t.n0 + cta_rank * load_n);
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
                 bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
@@ -298,13 +306,20 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 #endif
                 if (elect_one()) {
                     if (need_a || need_b) {
-                        mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_bytes : 0u));
+                        // fused gate/up activation: the scale words of the gate rows and of the up rows come as two boxes of
+                        // block_n / 2 words (one word per row and stage: per-128 scales only)
+                        const uint32_t sfb_tx = kOut == kOutSwiGluFp8 ? block_n * 4 : sfb_bytes;
+                        mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_tx : 0u));
                         if (need_a)
                             tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, row_a,
                                         static_cast<int32_t>(t.ga * p.sf_a_cols + kb / plan_a.period * plan_a.words));
-                        if (need_b)
-                            tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0),
-                                        static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words));
+                        if (need_b) {
+                            const int32_t sf_y = static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words);
+                            tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0), sf_y);
+                            if constexpr (kOut == kOutSwiGluFp8)
+                                tma_load_2d(smem_sfb + stage * sfb_bytes + block_n * 2, &tmap_sfb, bar_sf_raw + stage,
+                                            static_cast<int32_t>(t.n0 + p.n), sf_y);
+                        }
                     }
                     const uint32_t tx_bytes = (a_bytes >> p.tx_shift_a) + (b_bytes >> p.tx_shift_b);
                     if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, tx_bytes);
@@ -509,6 +524,62 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     else mbar_arrive_remote(bar_tmem_empty + e, 0);
                 }
             };
+            if constexpr (kOut == kOutSwiGluFp8) {
+                // accumulator columns [0, block_n / 2) are gate, [block_n / 2, block_n) up, for the same output columns.
+                // Per 32 output columns: both halves to registers, round to bf16 (what an unfused GEMM would have stored),
+                // act = bf16(silu(gate) * up), one power-of-two scale for the 32 values, e4m3, 32-byte rows staged for a
+                // TMA store, the scale byte straight to the packed scale words of the next GEMM's operand.
+                const uint32_t half_n = block_n / 2, num_out_subs = half_n / 32;
+                for (uint32_t s = 0; s < num_out_subs; ++s) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32b_x32(taddr + s * 32, g);
+                    tmem_ld_32x32b_x32(taddr + half_n + s * 32, u);
+                    tmem_ld_wait_x32(g);
+                    tmem_ld_wait_x32(u);
+                    if (s + 1 == num_out_subs) release_accumulator();
+                    uint8_t* buf = buf0 + buf_idx * kEpiBufBytes;
+                    if (lane == 0) tma_store_wait_read<1>();   // the store issued two buffers ago has finished reading this buffer
+                    __syncwarp();
+                    uint32_t amax = 0;
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 32; i += 2) {
+                        const uint32_t gb = pack_bf16x2(__uint_as_float(g[i]), __uint_as_float(g[i + 1]));
+                        const uint32_t ub = pack_bf16x2(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
+                        const float2 act = silu_mul_bf16x2(make_float2(__uint_as_float(gb << 16), __uint_as_float(gb & 0xFFFF0000u)),
+                                                           make_float2(__uint_as_float(ub << 16), __uint_as_float(ub & 0xFFFF0000u)));
+                        g[i] = __float_as_uint(act.x);         // bf16 values, widened
+                        g[i + 1] = __float_as_uint(act.y);
+                        amax = max(amax, max((g[i] >> 16) & 0x7FFFu, (g[i + 1] >> 16) & 0x7FFFu));
+                    }
+                    const uint32_t rounded = (amax + 0x7Fu - 0x60u) >> 7;
+                    uint32_t sf_exp = (rounded < 8u ? 8u : rounded) - 8u;
+                    sf_exp = sf_exp < 105u ? 105u : sf_exp;
+                    const float inv = __uint_as_float((254u - sf_exp) << 23);
+                    const uint32_t row_addr = smem_u32(buf) + lane * 32;
+                    #pragma unroll
+                    for (uint32_t j = 0; j < 2; ++j) {
+                        uint32_t w[4];
+                        #pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q)
+                            w[q] = cvt_e4m3x4(scale_pos_zero(__uint_as_float(g[16 * j + 4 * q + 0]), inv), scale_pos_zero(__uint_as_float(g[16 * j + 4 * q + 1]), inv),
+                                              scale_pos_zero(__uint_as_float(g[16 * j + 4 * q + 2]), inv), scale_pos_zero(__uint_as_float(g[16 * j + 4 * q + 3]), inv));
+                        st_shared_v4(row_addr + j * 16, w[0], w[1], w[2], w[3]);
+                    }
+                    const uint32_t col0 = t.n0 + s * 32;
+                    if (row < t.m_end && col0 < p.n)
+                        reinterpret_cast<uint8_t*>(p.sfd)[(static_cast<size_t>(t.ga * (p.n / 128) + col0 / 128) * p.sfd_stride + row) * 4 + (col0 % 128) / 32] =
+                            static_cast<uint8_t>(sf_exp);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (col0 < p.n && row0 < t.m_end)
+                            tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.gd));
+                        tma_store_commit();
+                    }
+                    buf_idx ^= 1;
+                }
+                continue;
+            }
             auto process = [&](uint32_t (&v)[32], uint32_t s) {
                 const uint32_t sub_in_buf = s % kSubsPerBuf;
                 uint8_t* buf = buf0 + buf_idx * kEpiBufBytes;

@@ -61,7 +61,13 @@ typedef struct {
 } dg_lp_operand;
 
 /* ops_sm100.rs:95-110 (Sm100Out) */
-enum { DG_OUT_BF16 = 0, DG_OUT_F32 = 1, DG_OUT_FP8 = 2 };
+/* DG_OUT_SWIGLU_FP8 (no counterpart as one call in the reference: moe.rs:254-296 runs the gate/up GEMM, then
+ * deepgemm_silu_mul_bf16, and would then have to quantise): b holds, per group, n gate rows followed by n up rows
+ * (b.rows = groups * 2n); the output is e4m3(silu(gate) * up), (rows, n) bytes at buf, with one UE8M0 scale per 32
+ * columns in sfd, laid out as for DG_OUT_FP8 -- i.e. the next GEMM's A operand with gran_k = 32.  The gate and up products
+ * are rounded to bf16 before the activation, as the unfused sequence does.  e4m3 operands, per-128 weight scales,
+ * n a multiple of 128; accepted by every GEMM entry point. */
+enum { DG_OUT_BF16 = 0, DG_OUT_F32 = 1, DG_OUT_FP8 = 2, DG_OUT_SWIGLU_FP8 = 3 };
 typedef struct {
     int kind;
     void* buf;            /* device; (rows, ld) elements of the kind */

@@ -434,6 +434,76 @@ def test_dense_mixed_fp8_fp4(ctx, m, n, k, a_bits, b_bits, gran8):
     assert O.calc_diff(to_f32(d), want) <= TIGHT_F32
 
 
+def fused_activation_reference(h):
+    """bf16 gate|up GEMM output (torch, (rows, 2n)) -> what the fused epilogue must write: the oracle's silu * up on those
+    bf16 bits, then its e4m3 quantiser with one scale per 32 columns."""
+    h_bits = h.view(torch.int16).cpu().numpy().view(np.uint16)
+    n = h_bits.shape[1] // 2
+    return O.cast_bf16_to_fp8_sf(O.silu_mul_bf16(h_bits), n, 32)
+
+
+@pytest.mark.parametrize("block_n", [0, 64, 128, 192, 256])
+def test_fused_gate_up_activation_dense(ctx, block_n, monkeypatch):
+    # out kind 3: B = [gate rows; up rows]; the GEMM writes e4m3(silu(gate) * up) + per-32 scales.  Must equal, bit for bit,
+    # the unfused sequence on the same operands: bf16 GEMM output -> silu * up -> quantise (the oracle's two steps)
+    m, n, k = 300, 384, 1152
+    _, aq, asf = fp8_operand_1d(m, k, 71)
+    _, bq, bsf = fp8_operand_1d(2 * n, k, 72)
+    a, b = lp(aq, asf, m, k), lp(bq, bsf, 2 * n, k)
+    h = torch.zeros((m, 2 * n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.Bf16(h, 2 * n))
+    ctx.sync()
+    want_q, want_sf = fused_activation_reference(h)
+    if block_n:
+        monkeypatch.setenv("DG_BLOCK_N", str(block_n))
+    q = torch.full((m, n), 0xAB, dtype=torch.uint8, device="cuda")
+    sfd = torch.zeros(dg.sf_packed_cols(n, 32) * dg.sf_aligned_rows(m), dtype=torch.int32, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.SwiGluFp8(q, n, sfd))
+    ctx.sync()
+    assert np.array_equal(q.cpu().numpy(), want_q)
+    assert np.array_equal(sfd.cpu().numpy().view(np.uint32), want_sf)
+
+
+@pytest.mark.parametrize("alignment", [128, 32])
+def test_fused_gate_up_activation_grouped_feeds_the_down_gemm(ctx, alignment):
+    sizes, n, k, n2 = [200, 0, 300, 129, 31], 256, 640, 320
+    groups = len(sizes)
+    m_idx, _ = contiguous_layout(sizes, alignment)
+    m_total = len(m_idx)
+    _, aq, asf = fp8_operand_1d(m_total, k, 73)
+    _, bq, bsf = fp8_operand_1d(groups * 2 * n, k, 74, 128, groups)
+    _, wq, wsf = fp8_operand_1d(groups * n2, n, 75, 128, groups)
+    a, b = lp(aq, asf, m_total, k), lp(bq, bsf, groups * 2 * n, k)
+    valid = np.nonzero(m_idx >= 0)[0]
+    dg.set_mk_alignment_for_contiguous_layout(alignment)
+    try:
+        h = torch.zeros((m_total, 2 * n), dtype=torch.bfloat16, device="cuda")
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, dev(m_idx), b, dg.Sm100Out.Bf16(h, 2 * n), groups)
+        ctx.sync()
+        want_q, want_sf = fused_activation_reference(h)
+        q = torch.zeros((m_total, n), dtype=torch.uint8, device="cuda")
+        sfd = torch.zeros(dg.sf_packed_cols(n, 32) * dg.sf_aligned_rows(m_total), dtype=torch.int32, device="cuda")
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a, dev(m_idx), b, dg.Sm100Out.SwiGluFp8(q, n, sfd), groups)
+        ctx.sync()
+        assert np.array_equal(q.cpu().numpy()[valid], want_q[valid])
+        got_sf = sfd.cpu().numpy().view(np.uint32).reshape(-1, dg.sf_aligned_rows(m_total))
+        assert np.array_equal(got_sf[:, valid], want_sf.reshape(got_sf.shape)[:, valid])
+        # the activation is the down projection's operand as it is (per-32 scales)
+        y = torch.zeros((m_total, n2), dtype=torch.bfloat16, device="cuda")
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(q, sfd, m_total, n, n, 8, 32), dev(m_idx), lp(wq, wsf, groups * n2, n),
+                                                 dg.Sm100Out.Bf16(y, n2), groups)
+        ctx.sync()
+        yn = to_f32(y)
+        q_np, sf_np = q.cpu().numpy(), sfd.cpu().numpy().view(np.uint32)
+        for g in range(groups):
+            rows = valid[m_idx[valid] == g].astype(np.uint32)
+            if rows.size:
+                want = O.lp_gemm_rows(q_np, sf_np, 8, 32, 1, m_total, rows, wq, wsf, 8, 128, groups, n2, np.arange(g * n2, (g + 1) * n2, dtype=np.uint32), n)
+                assert O.calc_diff(yn[rows.astype(np.int64)], want) <= TIGHT_BF16
+    finally:
+        dg.set_mk_alignment_for_contiguous_layout(128)
+
+
 def test_fp4_convenience_entry_points(ctx):
     # ops_sm100.rs:1646 / :1693: bf16 host tensors -> quantise -> MXF4 GEMM -> bf16 host result; equals the oracle's
     # quantiser followed by its f64 MXFP4 reference, to bf16 rounding
