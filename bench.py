@@ -274,7 +274,7 @@ class DenseWork:
 class MoeWork:
     """Expert-parallel contiguous grouped GEMM pair (see the module docstring)."""
 
-    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer", chunks=1, blocks_per_sm=2, fused_act=True):
+    def __init__(self, torch, dist, dg, ctx, dev, rank, world, exchange="peer", chunks=1, blocks_per_sm=2, fused_act=False):
         from deepgemm_rust_b200.moe_ep import DeviceRowOps, ExpertParallel, PeerExpertParallel, PipelinedPeerMoe
         self.torch, self.dg, self.ctx, self.dev, self.world = torch, dg, ctx, dev, world
         c = self.c = dict(MOE)
@@ -557,7 +557,7 @@ def run_config_table(args, torch, dg, ctx, dev, peaks):
     for experts in (MOE["experts"], MOE["experts"] // 8):
         saved = dict(MOE)
         MOE["experts"] = experts
-        moe = MoeWork(torch, None, dg, ctx, dev, 0, 1, "peer", fused_act=False)
+        moe = MoeWork(torch, None, dg, ctx, dev, 0, 1, "peer")
         MOE.update(saved)
         pe, c = moe.peer, moe.c
         a_op, ends = pe.dispatch(moe.topi, moe.xq, moe.xsf)
@@ -602,8 +602,9 @@ def main():
                     help="token micro-batches of the MoE step whose exchange overlaps the other micro-batches' GEMMs (measured slower "
                          "than 1 on 2 and 4 GPUs: the GEMMs lose more to the exchange kernels sharing their SMs than the overlap returns)")
     ap.add_argument("--ep-blocks-per-sm", type=int, default=2, help="grid bound of the exchange kernels when they run beside the GEMMs")
-    ap.add_argument("--unfused-act", action="store_true",
-                    help="MoE step: gate/up GEMM writes bf16 and a separate kernel applies silu(gate)*up and quantises (default: fused into the GEMM's epilogue)")
+    ap.add_argument("--fused-act", action="store_true",
+                    help="MoE step: silu(gate)*up and its quantiser run in the gate/up GEMM's epilogue (output kind DG_OUT_SWIGLU_FP8) instead of "
+                         "a kernel of their own; measured slower: the 192-wide tile it needs costs the GEMM more than the kernel it saves")
     ap.add_argument("--moe-tokens", type=int, default=None, help="moe_ep: tokens per rank (default 8192); smaller values for profiling captures")
     ap.add_argument("--only", default=None, help="M,N,K: run just this dense GEMM (profiling captures); implies --workload dense_fp8")
     args = ap.parse_args()
@@ -644,7 +645,7 @@ def main():
     # ---- build the workload (untimed): operands resident in HBM, quantised by the library's own kernels
     dense = DenseWork(torch, dg, ctx, dev, 1000 + rank) if args.workload in ("dsv3", "dense_fp8") else None
     chunks = max(1, args.moe_chunks)
-    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep, chunks, args.ep_blocks_per_sm, not args.unfused_act) if args.workload in ("dsv3", "moe_ep") else None
+    moe = MoeWork(torch, dist, dg, ctx, dev, rank, world, args.ep, chunks, args.ep_blocks_per_sm, args.fused_act) if args.workload in ("dsv3", "moe_ep") else None
     ctx.sync()
 
     def step(record=None):
