@@ -321,10 +321,13 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                                             static_cast<int32_t>(t.n0 + p.n), sf_y);
                         }
                     }
-                    const uint32_t tx_bytes = (a_bytes >> p.tx_shift_a) + (b_bytes >> p.tx_shift_b);
-                    if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, tx_bytes);
+                    const uint32_t a_tx = a_bytes >> p.tx_shift_a, b_tx = b_bytes >> p.tx_shift_b;
+                    // a pair's second CTA whose 128 rows all lie past the end of the group (or of the matrix) loads no A rows: its
+                    // accumulator rows are never stored, and the operand stream from L2 is what bounds these tiles
+                    const bool load_a = kCtas == 1 || static_cast<uint32_t>(row_a) < t.m_end;
+                    if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, a_tx + b_tx);
                     // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
-                    else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * tx_bytes);
+                    else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, (t.m0 + kBlockM < t.m_end ? 2u : 1u) * a_tx + 2 * b_tx);
                     for (uint32_t h = 0; h < halves; ++h) {
                         const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
                         uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
@@ -334,7 +337,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                             tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
                         } else {
                             const uint32_t bar_addr = full_bar_leader + stage * 8;
-                            tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
+                            if (load_a) tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
                             tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
                         }
                     }
