@@ -129,7 +129,7 @@ struct Scheduler {
             const int32_t valid = static_cast<int32_t>(__ldg(p.grouped_layout + cur_group));
             const uint32_t rows = valid <= 0 ? 0u : (static_cast<uint32_t>(valid) < p.m ? static_cast<uint32_t>(valid) : p.m);
             cur_row_start = 0;
-            cur_row_end = p.m;
+            cur_row_end = rows;      // nothing is stored (and a pair's second CTA loads nothing) past the group's valid rows
             cur_m_blocks = (rows + tile_m - 1) / tile_m;
         }
     }
