@@ -232,7 +232,15 @@ DG_DEVICE void ep_dispatch_pair(const EpDispatchParams& p, uint64_t pair, uint32
     uint4* dst = reinterpret_cast<uint4*>(p.peer_data[owner] + static_cast<size_t>(row) * p.k);
     const uint32_t vecs = p.k / 16;
     uint32_t c = lane;
-    for (; c + 96 < vecs; c += 128) {      // four loads in flight per lane
+    constexpr uint32_t kDeep = 8;          // loads in flight per lane before the first store (4 KB per warp)
+    for (; c + 32 * (kDeep - 1) < vecs; c += 32 * kDeep) {
+        uint4 v[kDeep];
+        #pragma unroll
+        for (uint32_t i = 0; i < kDeep; ++i) v[i] = __ldg(src + c + 32 * i);
+        #pragma unroll
+        for (uint32_t i = 0; i < kDeep; ++i) dst[c + 32 * i] = v[i];
+    }
+    for (; c + 96 < vecs; c += 128) {
         const uint4 v0 = __ldg(src + c), v1 = __ldg(src + c + 32), v2 = __ldg(src + c + 64), v3 = __ldg(src + c + 96);
         dst[c] = v0; dst[c + 32] = v1; dst[c + 64] = v2; dst[c + 96] = v3;
     }
@@ -271,13 +279,14 @@ __global__ void __launch_bounds__(256) dg_ep_combine_kernel(const EpCombineParam
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     const uint32_t t = i / chunks, c = i - t * chunks;
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (uint32_t j0 = 0; j0 < p.topk; j0 += 4) {
-        // up to four independent peer loads in flight before the first use
-        uint4 v[4];
-        float wj[4];
-        bool live[4];
+    constexpr uint32_t kDeep = 8;
+    for (uint32_t j0 = 0; j0 < p.topk; j0 += kDeep) {
+        // up to eight independent peer loads in flight before the first use
+        uint4 v[kDeep];
+        float wj[kDeep];
+        bool live[kDeep];
         #pragma unroll
-        for (uint32_t u = 0; u < 4; ++u) {
+        for (uint32_t u = 0; u < kDeep; ++u) {
             const uint32_t j = j0 + u;
             live[u] = false;
             if (j < p.topk) {
@@ -292,7 +301,7 @@ __global__ void __launch_bounds__(256) dg_ep_combine_kernel(const EpCombineParam
             }
         }
         #pragma unroll
-        for (uint32_t u = 0; u < 4; ++u) {
+        for (uint32_t u = 0; u < kDeep; ++u) {
             if (!live[u]) continue;
             const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
             #pragma unroll
