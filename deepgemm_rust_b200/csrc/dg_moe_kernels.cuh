@@ -182,17 +182,33 @@ __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __re
         before_me[e] = before;
     }
     __syncthreads();
-    for (uint32_t owner = threadIdx.x; owner < world; owner += blockDim.x) {
-        uint32_t row = 0, valid = 0;
-        for (uint32_t l = 0; l < local; ++l) {
-            const uint32_t e = owner * local + l;
-            start_of[e] = row;
-            if (owner == rank) group_ends[l] = row + rows_of[e];
-            valid += rows_of[e];
-            row += (rows_of[e] + alignment - 1) / alignment * alignment;
+    // one warp per owner: padded group sizes scanned 32 experts at a time
+    const uint32_t lane = threadIdx.x % 32;
+    for (uint32_t owner = threadIdx.x / 32; owner < world; owner += blockDim.x / 32) {
+        uint32_t running = 0, valid = 0;
+        for (uint32_t l0 = 0; l0 < local; l0 += 32) {
+            const uint32_t l = l0 + lane, e = owner * local + l;
+            const uint32_t r = l < local ? rows_of[e] : 0u;
+            const uint32_t padded = (r + alignment - 1) / alignment * alignment;
+            uint32_t inc = padded, sum_r = r;
+            #pragma unroll
+            for (uint32_t d = 1; d < 32; d *= 2) {
+                const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+                if (lane >= d) inc += up;
+                sum_r += __shfl_xor_sync(0xFFFFFFFFu, sum_r, d);
+            }
+            if (l < local) {
+                const uint32_t start = running + inc - padded;
+                start_of[e] = start;
+                if (owner == rank) group_ends[l] = start + r;
+            }
+            running += __shfl_sync(0xFFFFFFFFu, inc, 31);
+            valid += sum_r;
         }
-        arena_rows[owner] = row;
-        if (owner == rank) { totals[0] = row; totals[1] = valid; }
+        if (lane == 0) {
+            arena_rows[owner] = running;
+            if (owner == rank) { totals[0] = running; totals[1] = valid; }
+        }
     }
     __syncthreads();
     for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) pair_base[e] = start_of[e] + before_me[e];
