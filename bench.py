@@ -804,6 +804,9 @@ def main():
             line["cpu_baseline"] = {"value": cpu_sample_flops(cases) / sec / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                                     "sample": f"{CPU_SAMPLE_TEXT}, one pass ({sec:.1f} s)"}
         print(json.dumps(line), flush=True)
+    if moe is not None and moe.peer is not None:
+        # unmap the peers' buffers and free this rank's, in step with the other ranks, before the process group goes away
+        (moe.pipe or moe.peer).close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
