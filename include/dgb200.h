@@ -66,7 +66,7 @@ typedef struct {
  * (b.rows = groups * 2n); the output is e4m3(silu(gate) * up), (rows, n) bytes at buf, with one UE8M0 scale per 32
  * columns in sfd, laid out as for DG_OUT_FP8 -- i.e. the next GEMM's A operand with gran_k = 32.  The gate and up products
  * are rounded to bf16 before the activation, as the unfused sequence does.  e4m3 operands, per-128 weight scales,
- * n a multiple of 128; accepted by every GEMM entry point. */
+ * n a multiple of 128.  Exercised through the dense and the contiguous grouped entry points. */
 enum { DG_OUT_BF16 = 0, DG_OUT_F32 = 1, DG_OUT_FP8 = 2, DG_OUT_SWIGLU_FP8 = 3 };
 typedef struct {
     int kind;
