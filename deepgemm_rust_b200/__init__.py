@@ -120,9 +120,9 @@ _peer_close = _proto("dg_peer_close", C.c_int, _vp, _vp)
 _peer_free = _proto("dg_peer_free", C.c_int, _vp, _vp)
 _ep_hist_words = _proto("dg_ep_block_hist_words", _sz, _u32, _u32)
 _ep_count = _proto("dg_ep_count", C.c_int, _vp, _vp, _u32, _u32, _vp, _vp, _vp)
-_ep_layout = _proto("dg_ep_layout", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp)
+_ep_layout = _proto("dg_ep_layout", C.c_int, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _u32, _vp, _vp, _vp)
 _ep_dispatch = _proto("dg_ep_dispatch", C.c_int, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u32, _vp, _u32, _u32, _vp, _vp, _u32,
-                      _u32, _vp, _u32)
+                      _u32, _u32, _vp, _u32)
 _ep_combine = _proto("dg_ep_combine", C.c_int, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _sz, _u32, _vp, _sz, _u32)
 _expire_wait = _proto("dg_debug_expire_wait", C.c_int, _vp, _u32)
 _set_mk = _proto("dg_set_mk_alignment_for_contiguous_layout", C.c_int, _u32)
@@ -562,17 +562,17 @@ def ep_count_dev(ctx, expert_of_pair, pairs, num_experts, local_rank, block_hist
                      _vp(counts.data_ptr())))
 
 
-def ep_layout_dev(ctx, all_counts, world, rank, num_experts, alignment, capacity, pair_base, group_ends, totals):
-    _check(_ep_layout(ctx._h, _vp(all_counts.data_ptr()), world, rank, num_experts, alignment, capacity, _vp(pair_base.data_ptr()),
+def ep_layout_dev(ctx, all_counts, world, rank, num_experts, alignment, capacity, pair_base, group_ends, totals, slot_rows=0):
+    _check(_ep_layout(ctx._h, _vp(all_counts.data_ptr()), world, rank, num_experts, alignment, capacity, slot_rows, _vp(pair_base.data_ptr()),
                       _vp(group_ends.data_ptr()), _vp(totals.data_ptr())))
 
 
 def ep_dispatch_dev(ctx, expert_of_pair, local_rank, block_base, pair_base, pairs, topk, num_experts, world, data, k, sf, sf_stride, sf_cols,
-                    peer_data, peer_sf, peer_sf_stride, capacity, pos_of_pair, max_blocks=0):
+                    peer_data, peer_sf, peer_sf_stride, capacity, pos_of_pair, max_blocks=0, slot_rows=0):
     _check(_ep_dispatch(ctx._h, _vp(expert_of_pair.data_ptr()), _vp(local_rank.data_ptr()), _vp(block_base.data_ptr()),
                         _vp(pair_base.data_ptr()), pairs, topk, num_experts, world, _vp(data.data_ptr()), k, _vp(sf.data_ptr()), sf_stride,
-                        sf_cols, _vp(peer_data.data_ptr()), _vp(peer_sf.data_ptr()), peer_sf_stride, capacity, _vp(pos_of_pair.data_ptr()),
-                        max_blocks))
+                        sf_cols, _vp(peer_data.data_ptr()), _vp(peer_sf.data_ptr()), peer_sf_stride, capacity, slot_rows,
+                        _vp(pos_of_pair.data_ptr()), max_blocks))
 
 
 def ep_combine_dev(ctx, expert_of_pair, pos_of_pair, weights, tokens, topk, num_experts, world, peer_rows, pitch, n, out, out_pitch,

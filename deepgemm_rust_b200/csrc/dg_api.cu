@@ -1059,14 +1059,14 @@ int dg_ep_count(dg_ctx* ctx, const int32_t* expert_of_pair, uint32_t pairs, uint
 }
 
 int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32_t rank, uint32_t num_experts, uint32_t alignment,
-                 uint32_t capacity, uint32_t* pair_base, uint32_t* group_ends, uint32_t* totals) {
+                 uint32_t capacity, uint32_t slot_rows, uint32_t* pair_base, uint32_t* group_ends, uint32_t* totals) {
     if (!ctx || !all_counts || !pair_base || !group_ends || !totals) return fail(DG_ERR_SHAPE, "null argument");
     if (world == 0 || world > 1024 || rank >= world || num_experts == 0 || num_experts > 4096 || num_experts % world != 0)
         return fail(DG_ERR_SHAPE, "need 1 <= world <= 1024, rank < world, num_experts <= 4096 and a multiple of world");
     if (alignment == 0) return fail(DG_ERR_SHAPE, "alignment must be positive");
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     dg::dg_ep_layout_kernel<<<1, 1024, 3 * num_experts * sizeof(uint32_t), ctx->stream>>>(all_counts, world, rank, num_experts, alignment, capacity,
-                                                                                         pair_base, group_ends, totals);
+                                                                                         slot_rows, pair_base, group_ends, totals);
     DG_CUDA(cudaGetLastError());
     return DG_OK;
 }
@@ -1074,13 +1074,13 @@ int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32
 int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* local_rank, const uint32_t* block_base, const uint32_t* pair_base,
                    uint32_t pairs, uint32_t topk, uint32_t num_experts, uint32_t world, const uint8_t* data, uint32_t k, const uint32_t* sf,
                    uint32_t sf_stride, uint32_t sf_cols, void* const* peer_data, void* const* peer_sf, uint32_t peer_sf_stride,
-                   uint32_t capacity, int32_t* pos_of_pair, uint32_t max_blocks) {
+                   uint32_t capacity, uint32_t slot_rows, int32_t* pos_of_pair, uint32_t max_blocks) {
     if (!ctx || !expert_of_pair || !local_rank || !block_base || !pair_base || !data || !sf || !peer_data || !peer_sf || !pos_of_pair)
         return fail(DG_ERR_SHAPE, "null argument");
     if (k % 16 || !aligned16(data)) return fail(DG_ERR_SHAPE, "k and the token rows must be multiples of 16 bytes");
     if (topk == 0 || pairs % topk != 0) return fail(DG_ERR_SHAPE, "pairs (%u) must be tokens x topk (%u)", pairs, topk);
     if (world == 0 || num_experts % world != 0) return fail(DG_ERR_SHAPE, "num_experts (%u) must be a multiple of world (%u)", num_experts, world);
-    if (peer_sf_stride < capacity) return fail(DG_ERR_SHAPE, "arena scale stride smaller than the arena capacity");
+    if (peer_sf_stride < (slot_rows ? slot_rows : capacity)) return fail(DG_ERR_SHAPE, "arena scale stride smaller than the rows it indexes");
     if (pairs == 0) return DG_OK;
     dg::EpDispatchParams p;
     p.expert_of_pair = expert_of_pair; p.local_rank = local_rank; p.block_base = block_base; p.pair_base = pair_base;
@@ -1088,7 +1088,7 @@ int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* lo
     p.peer_data = reinterpret_cast<uint8_t* const*>(peer_data); p.peer_sf = reinterpret_cast<uint32_t* const*>(peer_sf);
     p.pos_of_pair = pos_of_pair;
     p.pairs = pairs; p.topk = topk; p.k = k; p.sf_cols = sf_cols; p.sf_stride = sf_stride; p.peer_sf_stride = peer_sf_stride;
-    p.num_experts = num_experts; p.experts_per_rank = num_experts / world; p.capacity = capacity;
+    p.num_experts = num_experts; p.experts_per_rank = num_experts / world; p.capacity = capacity; p.slot_rows = slot_rows;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     uint32_t blocks = ceil_div(pairs, 8);
     if (max_blocks != 0 && blocks > max_blocks) blocks = max_blocks;

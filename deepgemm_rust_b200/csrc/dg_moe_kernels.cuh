@@ -162,8 +162,11 @@ __global__ void __launch_bounds__(256) dg_ep_block_scan_kernel(uint32_t* __restr
 //   totals[0..3]   arena rows in use on this rank (groups padded to `alignment`), valid rows on this
 //                  rank, 1 if any owner's arena would exceed `capacity` rows (dispatch then drops the
 //                  rows that do not fit), largest arena in use on any rank
+// slot_rows != 0 selects the masked layout instead: local expert l owns the fixed slot of rows [l * slot_rows,
+// (l + 1) * slot_rows), group_ends[l] is then its valid row count (the masked GEMM's masked_m), and the overflow flag is
+// raised when some expert receives more than slot_rows rows (or the slots exceed `capacity`).
 __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __restrict__ all_counts, uint32_t world, uint32_t rank, uint32_t num_experts,
-                                                            uint32_t alignment, uint32_t capacity, uint32_t* __restrict__ pair_base,
+                                                            uint32_t alignment, uint32_t capacity, uint32_t slot_rows, uint32_t* __restrict__ pair_base,
                                                             uint32_t* __restrict__ group_ends, uint32_t* __restrict__ totals) {
     extern __shared__ uint32_t ep_smem[];
     uint32_t* rows_of = ep_smem;                  // [num_experts] rows of the expert over all source ranks
@@ -182,6 +185,9 @@ __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __re
         before_me[e] = before;
     }
     __syncthreads();
+    __shared__ uint32_t slot_overflow;
+    if (threadIdx.x == 0) slot_overflow = 0;
+    __syncthreads();
     // one warp per owner: padded group sizes scanned 32 experts at a time
     const uint32_t lane = threadIdx.x % 32;
     for (uint32_t owner = threadIdx.x / 32; owner < world; owner += blockDim.x / 32) {
@@ -189,7 +195,8 @@ __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __re
         for (uint32_t l0 = 0; l0 < local; l0 += 32) {
             const uint32_t l = l0 + lane, e = owner * local + l;
             const uint32_t r = l < local ? rows_of[e] : 0u;
-            const uint32_t padded = (r + alignment - 1) / alignment * alignment;
+            const uint32_t padded = slot_rows ? (l < local ? slot_rows : 0u) : (r + alignment - 1) / alignment * alignment;
+            if (slot_rows && r > slot_rows) slot_overflow = 1;
             uint32_t inc = padded, sum_r = r;
             #pragma unroll
             for (uint32_t d = 1; d < 32; d *= 2) {
@@ -200,7 +207,7 @@ __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __re
             if (l < local) {
                 const uint32_t start = running + inc - padded;
                 start_of[e] = start;
-                if (owner == rank) group_ends[l] = start + r;
+                if (owner == rank) group_ends[l] = slot_rows ? r : start + r;
             }
             running += __shfl_sync(0xFFFFFFFFu, inc, 31);
             valid += sum_r;
@@ -215,7 +222,7 @@ __global__ void __launch_bounds__(1024) dg_ep_layout_kernel(const uint32_t* __re
     if (threadIdx.x == 0) {
         uint32_t largest = 0;
         for (uint32_t s = 0; s < world; ++s) largest = arena_rows[s] > largest ? arena_rows[s] : largest;
-        totals[2] = largest > capacity ? 1u : 0u;
+        totals[2] = (largest > capacity || slot_overflow) ? 1u : 0u;
         totals[3] = largest;
     }
 }
@@ -234,6 +241,8 @@ struct EpDispatchParams {
     uint32_t* const* peer_sf;        // [world] arena scale words, sf[c * peer_sf_stride + row]
     int32_t* pos_of_pair;            // (pairs) arena row on the owner, -1 if dropped
     uint32_t pairs, topk, k, sf_cols, sf_stride, peer_sf_stride, num_experts, experts_per_rank, capacity;
+    uint32_t slot_rows;              // masked layout: rows per expert slot (0: contiguous layout); the arena's scale words are then
+                                     // laid out per slot, sf[(slot * sf_cols + c) * peer_sf_stride + row in slot]
 };
 
 DG_DEVICE void ep_dispatch_pair(const EpDispatchParams& p, uint64_t pair, uint32_t lane) {
@@ -241,9 +250,11 @@ DG_DEVICE void ep_dispatch_pair(const EpDispatchParams& p, uint64_t pair, uint32
     if (lr < 0) { if (lane == 0) p.pos_of_pair[pair] = -1; return; }
     const uint32_t e = static_cast<uint32_t>(__ldg(p.expert_of_pair + pair));
     const uint32_t row = __ldg(p.pair_base + e) + __ldg(p.block_base + (pair / kEpChunk) * p.num_experts + e) + static_cast<uint32_t>(lr);
-    if (row >= p.capacity) { if (lane == 0) p.pos_of_pair[pair] = -1; return; }
+    const uint32_t owner = e / p.experts_per_rank, slot = e - owner * p.experts_per_rank;
+    const uint32_t in_slot = row - slot * p.slot_rows;      // masked layout only
+    if (row >= p.capacity || (p.slot_rows != 0 && in_slot >= p.slot_rows)) { if (lane == 0) p.pos_of_pair[pair] = -1; return; }
     if (lane == 0) p.pos_of_pair[pair] = static_cast<int32_t>(row);
-    const uint32_t owner = e / p.experts_per_rank, tok = static_cast<uint32_t>(pair / p.topk);
+    const uint32_t tok = static_cast<uint32_t>(pair / p.topk);
     const uint4* src = reinterpret_cast<const uint4*>(p.data + static_cast<size_t>(tok) * p.k);
     uint4* dst = reinterpret_cast<uint4*>(p.peer_data[owner] + static_cast<size_t>(row) * p.k);
     const uint32_t vecs = p.k / 16;
@@ -262,8 +273,9 @@ DG_DEVICE void ep_dispatch_pair(const EpDispatchParams& p, uint64_t pair, uint32
     }
     for (; c < vecs; c += 32) dst[c] = __ldg(src + c);
     uint32_t* dsf = p.peer_sf[owner];
+    const size_t sf_base = p.slot_rows ? static_cast<size_t>(slot) * p.sf_cols * p.peer_sf_stride + in_slot : row;
     for (uint32_t w = lane; w < p.sf_cols; w += 32)
-        dsf[static_cast<size_t>(w) * p.peer_sf_stride + row] = __ldg(p.sf + static_cast<size_t>(w) * p.sf_stride + tok);
+        dsf[sf_base + static_cast<size_t>(w) * p.peer_sf_stride] = __ldg(p.sf + static_cast<size_t>(w) * p.sf_stride + tok);
 }
 
 

@@ -156,7 +156,8 @@ class PeerExpertParallel:
     """
 
     def __init__(self, ctx, num_experts: int, topk: int, max_tokens: int, hidden: int, out_n: int, gran: int = 128,
-                 group: Optional[dist.ProcessGroup] = None, alignment: int = 128, capacity: Optional[int] = None):
+                 group: Optional[dist.ProcessGroup] = None, alignment: int = 128, capacity: Optional[int] = None,
+                 slot_rows: int = 0):
         import deepgemm_rust_b200 as dg
         self.dg, self.ctx, self.group = dg, ctx, group
         self.distributed = dist.is_available() and dist.is_initialized() and (group is not None or dist.get_world_size() > 1)
@@ -168,13 +169,20 @@ class PeerExpertParallel:
         self.max_pairs, self.hidden, self.out_n, self.gran, self.alignment = max_tokens * topk, hidden, out_n, gran, alignment
         worst = self.world * self.max_pairs + alignment * self.local_experts
         cap = min(capacity, worst) if capacity else worst
+        # slot_rows: the masked layout (decode-style steps): every local expert owns a fixed slot of that many arena rows and
+        # `group_ends` holds the valid row count of each slot, i.e. the masked GEMM's masked_m with m_max = slot_rows
+        self.slot_rows = slot_rows
+        if slot_rows:
+            cap = slot_rows * self.local_experts
         self.capacity = cap = (cap + 127) // 128 * 128
-        self.sf_cols, self.sf_stride = dg.sf_packed_cols(hidden, gran), dg.sf_aligned_rows(cap)
+        self.sf_cols = dg.sf_packed_cols(hidden, gran)
+        self.sf_stride = dg.sf_aligned_rows(slot_rows) if slot_rows else dg.sf_aligned_rows(cap)
         dev = self.device = torch.device(f"cuda:{ctx.ordinal}")
 
         def region(nbytes):
             return (nbytes + 255) // 256 * 256
-        sizes = [region(cap * hidden), region(self.sf_cols * self.sf_stride * 4), region(cap * out_n * 2)]
+        sf_words = self.sf_cols * self.sf_stride * (self.local_experts if slot_rows else 1)
+        sizes = [region(cap * hidden), region(sf_words * 4), region(cap * out_n * 2)]
         offs = [0, sizes[0], sizes[0] + sizes[1]]
         self._base, handle = dg.peer_alloc(ctx, sum(sizes), export=self.distributed)
         self._opened = []
@@ -195,7 +203,7 @@ class PeerExpertParallel:
         self._peer_sf = torch.tensor([b + offs[1] for b in bases], dtype=torch.int64, device=dev)
         self._peer_rows = torch.tensor([b + offs[2] for b in bases], dtype=torch.int64, device=dev)
         self.arena = dg.tensor_from_ptr(self._base + offs[0], (cap, hidden), torch.uint8, ctx.ordinal)
-        self.arena_sf = dg.tensor_from_ptr(self._base + offs[1], (self.sf_cols * self.sf_stride,), torch.int32, ctx.ordinal)
+        self.arena_sf = dg.tensor_from_ptr(self._base + offs[1], (sf_words,), torch.int32, ctx.ordinal)
         self.result = dg.tensor_from_ptr(self._base + offs[2], (cap, out_n), torch.bfloat16, ctx.ordinal)
         self.arena.zero_()
         self.arena_sf.zero_()
@@ -220,7 +228,10 @@ class PeerExpertParallel:
             dist.all_reduce(self._fence_word, group=self.group)
 
     def operand(self):
-        """The arena as the grouped GEMMs' A: `capacity` rows, of which the group table bounds the work."""
+        """The arena as the grouped GEMMs' A: `capacity` rows, of which the group table bounds the work (masked layout: one
+        slot of `slot_rows` rows per local expert, as the masked GEMM wants it)."""
+        if self.slot_rows:
+            return self.dg.LpOperand(self.arena, self.arena_sf, self.slot_rows, self.hidden, self.hidden, 8, self.gran)
         return self.dg.LpOperand(self.arena, self.arena_sf, self.capacity, self.hidden, self.hidden, 8, self.gran)
 
     def dispatch(self, topk_idx: torch.Tensor, xq: torch.Tensor, xsf: torch.Tensor, sf_stride: Optional[int] = None):
@@ -238,10 +249,10 @@ class PeerExpertParallel:
         if self.distributed:
             dist.all_gather_into_tensor(self._all_counts, self._counts, group=self.group)
         dg.ep_layout_dev(ctx, self._all_counts, self.world, self.rank, self.num_experts, self.alignment, self.capacity, self._pair_base,
-                         self.group_ends, self.totals)
+                         self.group_ends, self.totals, self.slot_rows)
         dg.ep_dispatch_dev(ctx, self._experts, self._local_rank, self._block_hist, self._pair_base, pairs, topk, self.num_experts, self.world,
                            xq, self.hidden, xsf, sf_stride or dg.sf_aligned_rows(tokens), self.sf_cols, self._peer_data, self._peer_sf, self.sf_stride,
-                           self.capacity, self.pos_of_pair, self.max_blocks)
+                           self.capacity, self.pos_of_pair, self.max_blocks, self.slot_rows)
         self._fence()
         return self.operand(), self.group_ends
 

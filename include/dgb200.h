@@ -243,19 +243,25 @@ int dg_ep_count(dg_ctx* ctx, const int32_t* expert_of_pair, uint32_t pairs, uint
  * pair_base[e] = arena row of this rank's first pair for expert e; group_ends[l] (num_experts / world words) = one
  * past the last valid row of local expert l, the table dg_m_grouped_fp8_fp4_gemm_contiguous_ends takes;
  * totals[0..3] = arena rows in use here, valid rows here, 1 if some rank's arena needs more than `capacity` rows
- * (dispatch then drops the rows that do not fit, and combine skips them), the largest arena in use. */
+ * (dispatch then drops the rows that do not fit, and combine skips them), the largest arena in use.
+ * slot_rows != 0 selects the masked layout of ops_sm100.rs:815 instead (decode-style steps): local expert l owns rows
+ * [l * slot_rows, (l + 1) * slot_rows) of the arena, group_ends[l] becomes its valid row count (the masked_m array of
+ * dg_m_grouped_fp8_fp4_gemm_masked with m_max = slot_rows), and the flag is also raised when an expert receives more than
+ * slot_rows rows. */
 int dg_ep_layout(dg_ctx* ctx, const uint32_t* all_counts, uint32_t world, uint32_t rank, uint32_t num_experts, uint32_t alignment,
-                 uint32_t capacity, uint32_t* pair_base, uint32_t* group_ends, uint32_t* totals);
+                 uint32_t capacity, uint32_t slot_rows, uint32_t* pair_base, uint32_t* group_ends, uint32_t* totals);
 /* moe.rs:176-206 (gather of token rows and scale rows into the grouped layout), across ranks: pair p's e4m3 row
  * (k bytes) and its sf_cols scale words go to row pos_of_pair[p] of the arena of the rank that owns its expert.
  * peer_data / peer_sf: device arrays of `world` pointers (every rank's arena (capacity, k) and its scale words
  * sf[c * peer_sf_stride + row]), entry `rank` being the local buffers.  Padding rows are not written.
+ * slot_rows: as given to dg_ep_layout; in the masked layout the scale words go to the per-slot layout the masked GEMM
+ * reads, sf[(slot * sf_cols + c) * peer_sf_stride + row in slot] with peer_sf_stride = dg_sf_aligned_rows(slot_rows).
  * max_blocks: 0 launches one warp per pair; a positive value bounds the grid (256-thread blocks striding over the
  * pairs), e.g. 2 x the SM count to leave room on every SM for a GEMM running beside the exchange. */
 int dg_ep_dispatch(dg_ctx* ctx, const int32_t* expert_of_pair, const int32_t* local_rank, const uint32_t* block_base, const uint32_t* pair_base,
                    uint32_t pairs, uint32_t topk, uint32_t num_experts, uint32_t world, const uint8_t* data, uint32_t k, const uint32_t* sf,
                    uint32_t sf_stride, uint32_t sf_cols, void* const* peer_data, void* const* peer_sf, uint32_t peer_sf_stride,
-                   uint32_t capacity, int32_t* pos_of_pair, uint32_t max_blocks);
+                   uint32_t capacity, uint32_t slot_rows, int32_t* pos_of_pair, uint32_t max_blocks);
 /* moe.rs:314-360 (weighted scatter-accumulate and f32 -> bf16), across ranks and as a gather: out[t, :] =
  * bf16(sum_j weights[t, j] * rows_j[pos_of_pair[t, j], :]) with rows_j the result buffer (bf16, `pitch` elements per
  * row) of the rank owning expert_of_pair[t, j]; same arithmetic as dg_moe_combine.  max_blocks as for dg_ep_dispatch. */

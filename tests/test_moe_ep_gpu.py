@@ -291,3 +291,64 @@ def test_pair_ranking_is_a_stable_counting_sort(ctx):
             seen[ids[p]] += 1
         else:
             assert lr[p] == -1
+
+
+def test_peer_exchange_masked_layout(ctx):
+    # decode-style step: every local expert owns a fixed slot of rows, the exchange writes token rows and their scale words
+    # straight into the (experts, slot_rows, k) operand of the masked grouped GEMM and hands it the per-expert row counts
+    experts, topk, tokens, hidden, n, slot = 8, 2, 90, 512, 256, 64
+    g = torch.Generator().manual_seed(44)
+    topw, topi = torch.softmax(torch.randn((tokens, experts), generator=g), -1).topk(topk, dim=-1)
+    topi[topi == 2] = 3                                               # an empty slot
+    _, xq, xsf = fp8_operand_1d(tokens, hidden, 61)
+    _, wq, wsf, _ = fp8_operand_2d(experts * n, hidden, 62, experts)
+    pe = PeerExpertParallel(ctx, experts, topk, tokens, hidden, n, slot_rows=slot)
+    try:
+        a_op, masked_m = pe.dispatch(topi.cuda(), dev(xq), dev(xsf))
+        ctx.sync()
+        flat = topi.reshape(-1).numpy()
+        counts = np.bincount(flat, minlength=experts)
+        assert counts.max() <= slot and not pe.overflowed()
+        assert np.array_equal(masked_m.cpu().numpy(), counts)
+        pos = np.zeros(flat.size, np.int64)
+        seen = np.zeros(experts, np.int64)
+        for p, e in enumerate(flat):
+            pos[p] = e * slot + seen[e]
+            seen[e] += 1
+        assert np.array_equal(pe.pos_of_pair.cpu().numpy()[:pos.size], pos)
+        arena = pe.arena.cpu().numpy()
+        assert np.array_equal(arena[pos], xq[np.arange(flat.size) // topk])
+        cols = pe.sf_cols
+        sf = pe.arena_sf.cpu().numpy().view(np.uint32).reshape(experts, cols, dg.sf_aligned_rows(slot))
+        xsf2 = xsf.reshape(cols, -1)
+        assert np.array_equal(sf[pos // slot, :, pos % slot], xsf2[:, np.arange(flat.size) // topk].T)
+        dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, a_op, masked_m, dg.LpOperand(dev(wq), dev(wsf), experts * n, hidden, hidden),
+                                             dg.Sm100Out.Bf16(pe.result, n), experts, max(1, int(counts.mean())))
+        out = pe.combine(topw.cuda().contiguous())
+        ctx.sync()
+        # every valid result row against the oracle, then the reduction bit for bit
+        yn = to_f32(pe.result)
+        for e in range(experts):
+            rows = pos[flat == e].astype(np.uint32)
+            if rows.size:
+                want = O.lp_gemm_rows(arena, pe.arena_sf.cpu().numpy().view(np.uint32), 8, 128, experts, slot, rows, wq, wsf, 8, 128,
+                                      experts, n, np.arange(e * n, (e + 1) * n, dtype=np.uint32), hidden)
+                assert O.calc_diff(yn[rows.astype(np.int64)], want) <= 2e-5
+        y_bits = pe.result.view(torch.int16).cpu().numpy().view(np.uint16)
+        want = O.moe_combine(y_bits, pos.reshape(tokens, topk).astype(np.int32), topw.numpy())
+        assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), want)
+    finally:
+        pe.close()
+    # a slot too small for its expert: the rows that do not fit are dropped and flagged
+    pe = PeerExpertParallel(ctx, experts, topk, tokens, hidden, n, slot_rows=16)
+    try:
+        pe.dispatch(topi.cuda(), dev(xq), dev(xsf))
+        ctx.sync()
+        assert pe.overflowed()
+        got = pe.pos_of_pair.cpu().numpy()[:flat.size]
+        seen[:] = 0
+        for p, e in enumerate(flat):
+            assert got[p] == (e * 16 + seen[e] if seen[e] < 16 else -1)
+            seen[e] += 1
+    finally:
+        pe.close()

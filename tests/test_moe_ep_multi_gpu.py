@@ -79,6 +79,14 @@ def _rank_main(rank, world, port, results):
             torch.cuda.synchronize()
             ok = ok and bool(np.array_equal(out3.view(torch.int16).cpu().numpy().view(np.uint16), want))
         pipe.close()
+        # masked layout (decode-style): fixed slots per local expert, the masked grouped GEMM on the exchange's own buffers
+        pm = PeerExpertParallel(ctx, experts, topk, tokens, k, n, slot_rows=256)
+        a_op, masked_m = pm.dispatch(topi, xq, xsf)
+        dg.m_grouped_fp8_fp4_gemm_masked_dev(ctx, a_op, masked_m, w_local, dg.Sm100Out.Bf16(pm.result, n), local, 150)
+        out4 = pm.combine(topw)
+        ctx.sync()
+        ok = ok and bool(np.array_equal(out4.view(torch.int16).cpu().numpy().view(np.uint16), want)) and not pm.overflowed()
+        pm.close()
         results[rank] = ok
         ctx.close()
     finally:
