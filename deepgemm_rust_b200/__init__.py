@@ -89,6 +89,7 @@ _gemm_contig_ends = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_ends", C.c_int,
                            C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
 _gemm_contig_static = _proto("dg_m_grouped_fp8_fp4_gemm_contiguous_static", C.c_int, C.c_int, _vp, C.POINTER(_LpOperand), _vp,
                              C.POINTER(_LpOperand), C.POINTER(_Out), _u32, C.POINTER(_Epilogue))
+_static_check_status = _proto("dg_static_check_status", C.c_int, C.c_int, _vp)
 _bf16_gemm = _proto("dg_bf16_gemm", C.c_int, _vp, _vp, _u32, _u32, _vp, _u32, _u32, _u32, C.POINTER(_Out), C.POINTER(_Epilogue))
 _gemm_masked = _proto("dg_m_grouped_fp8_fp4_gemm_masked", C.c_int, _vp, C.POINTER(_LpOperand), _vp, C.POINTER(_LpOperand),
                       C.POINTER(_Out), _u32, _u32, C.POINTER(_Epilogue))
@@ -335,6 +336,12 @@ def m_grouped_fp8_fp4_gemm_contiguous_static_dev(device: int, cuda_stream: int, 
     ca, cb, co, ce = a._c(), b._c(), out._c(), _epi(epi)
     _check(_gemm_contig_static(device, _vp(cuda_stream), C.byref(ca), _vp(m_indices.data_ptr()), C.byref(cb), C.byref(co), num_groups,
                                C.byref(ce)))
+
+
+def static_check_status(device: int, cuda_stream: int):
+    """Waits for the stream, then raises DgError(Timeout) if a kernel of the allocation-free call gave up on a
+    device-side wait (and clears that record); the counterpart of DgContext.sync() for calls made without a context."""
+    _check(_static_check_status(device, _vp(cuda_stream)))
 
 
 def m_grouped_fp8_fp4_gemm_masked_dev(ctx, a, masked_m: torch.Tensor, b, out, num_groups: int, expected_m: int, epi=None):

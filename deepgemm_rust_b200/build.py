@@ -3,6 +3,7 @@
 `python deepgemm_rust_b200/build.py` (or build()) compiles csrc/dg_api.cu, which includes the
 kernel headers, into deepgemm_rust_b200/libdgb200.so.  nvcc cross-compiles without a GPU.
 """
+import glob
 import os
 import subprocess
 import sys
@@ -11,7 +12,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdgb200.so")
 SOURCES = ["dg_api.cu"]
-DEPS = ["dg_api.cu", "dg_gemm_kernel.cuh", "dg_cast_kernels.cuh", "dg_ptx.cuh", os.path.join("..", "..", "include", "dgb200.h")]
+
+
+def deps():
+    """Every source the library is compiled from: all of csrc/ plus the public header."""
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh"))) + [
+        os.path.join(HERE, "..", "include", "dgb200.h")]
+
+
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
          "-Xcompiler", "-fPIC,-fvisibility=default", "--expt-relaxed-constexpr"]
@@ -21,7 +29,7 @@ def needs_build() -> bool:
     if not os.path.exists(OUT):
         return True
     t = os.path.getmtime(OUT)
-    return any(os.path.getmtime(os.path.join(CSRC, d)) > t for d in DEPS)
+    return any(os.path.getmtime(d) > t for d in deps())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

@@ -370,18 +370,25 @@ cudaError_t launch_reduce(uint32_t blocks, cudaStream_t stream, const float* par
     return cudaLaunchKernelEx(&cfg, dg::dg_splitk_reduce_kernel<kBf16>, partial, splits, m, n, pitch, alpha, out, out_ld);
 }
 
+// The opt-in to the full shared-memory carve-out is per kernel instantiation and per device; the first
+// call also makes the runtime load that kernel's image.
 template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
-cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
-    auto kernel = dg::dg_gemm_kernel<kFmt, kOut, kCtas>;
-    // the opt-in is per device; remember which devices already have it
+cudaError_t configure_kernel() {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 64 || !(configured.load() & (1ull << dev))) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemCapacity));
-        if (e != cudaSuccess) return e;
-        if (dev < 64) configured.fetch_or(1ull << dev);
-    }
+    if (dev < 64 && (configured.load() & (1ull << dev))) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(dg::dg_gemm_kernel<kFmt, kOut, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(kSmemCapacity));
+    if (e == cudaSuccess && dev < 64) configured.fetch_or(1ull << dev);
+    return e;
+}
+
+template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
+cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
+    auto kernel = dg::dg_gemm_kernel<kFmt, kOut, kCtas>;
+    cudaError_t e = configure_kernel<kFmt, kOut, kCtas>();
+    if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid, 1, 1);
@@ -410,6 +417,26 @@ cudaError_t launch_by_out(int kind, const dg::GemmParams& p, uint32_t grid, uint
     if constexpr (kFmt != dg::kFmtBf16)
         if (kind == DG_OUT_FP8) return launch_kernel<kFmt, dg::kOutFp8, kCtas>(p, grid, smem, stream, maps);
     return cudaErrorInvalidValue;
+}
+
+template <uint32_t kFmt>
+cudaError_t configure_contiguous_kernels_of() {
+    cudaError_t e = cudaSuccess;
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutBf16, 1>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutBf16, 2>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutF32, 1>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutF32, 2>();
+    return e;
+}
+// Everything dg_m_grouped_fp8_fp4_gemm_contiguous[_ends] can launch, configured (and loaded) for the current device.
+cudaError_t configure_contiguous_kernels() {
+    cudaError_t e = configure_contiguous_kernels_of<dg::kFmtMxf8f6f4>();
+    if (e == cudaSuccess) e = configure_contiguous_kernels_of<dg::kFmtMxf4>();
+    if (e == cudaSuccess) e = configure_kernel<dg::kFmtMxf8f6f4, dg::kOutSwiGluFp8, 2>();
+    cudaFuncAttributes fa;
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, dg::dg_group_ends_kernel);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&fa, dg::dg_group_ends_scan_kernel);
+    return e;
 }
 
 int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, const dg_out* out, const dg_epilogue* epi, const Problem& pr) {
@@ -783,6 +810,9 @@ int static_device_setup(int device, StaticDevice** out) {
         uint32_t* ptr = nullptr;
         DG_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
         d.scratch = ptr;
+        // every kernel the contiguous path can reach gets its shared-memory opt-in (and its image loaded) now, so that later
+        // calls with another output kind, operand format or tile choice do no set-up work
+        DG_CUDA(configure_contiguous_kernels());
         d.ready = true;
     }
     *out = &d;
@@ -812,6 +842,24 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous_static(int device, void* cuda_stream, c
     rc = run_group_ends(&view, m_indices, a->rows, num_groups, ends);
     if (rc) return rc;
     return dg_m_grouped_fp8_fp4_gemm_contiguous_ends(&view, a, ends, b, out, num_groups, epi);
+}
+
+int dg_static_check_status(int device, void* cuda_stream) {
+    StaticDevice* dev = nullptr;
+    int rc = static_device_setup(device, &dev);
+    if (rc) return rc;
+    DG_CUDA(cudaSetDevice(device));
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    dg::Status st;
+    // a stack destination and 16 bytes: the copy allocates nothing; it is ordered after the GEMMs enqueued on `stream`
+    DG_CUDA(cudaMemcpyAsync(&st, dev->scratch, sizeof(st), cudaMemcpyDeviceToHost, stream));
+    DG_CUDA(cudaStreamSynchronize(stream));
+    if (st.code != 0) {
+        DG_CUDA(cudaMemsetAsync(dev->scratch, 0, sizeof(st), stream));
+        DG_CUDA(cudaStreamSynchronize(stream));
+        return fail(DG_ERR_TIMEOUT, "a device-side wait ran out: block %u, site 0x%x, parity %u", st.block, st.site, st.extra);
+    }
+    return DG_OK;
 }
 
 // ------------------------------------------------------------------ quantise / re-layout

@@ -153,6 +153,8 @@ class PeerExpertParallel:
     stale rows); the grouped GEMM computes them inside its tiles and stores none of them.
     Nothing in a step reads back to the host: the arena's row count stays on the device (`totals`), the grouped
     GEMMs take `group_ends`, and operands are declared with `capacity` rows.
+    The context's stream must be torch's current stream whenever dispatch() or combine() is called (checked): the
+    collectives between the ranks are ordered against that stream only.
     """
 
     def __init__(self, ctx, num_experts: int, topk: int, max_tokens: int, hidden: int, out_n: int, gran: int = 128,
@@ -225,7 +227,16 @@ class PeerExpertParallel:
     def _fence(self):
         """Orders the ranks on the stream: what each wrote before is visible to all after."""
         if self.distributed:
+            self._check_stream()
             dist.all_reduce(self._fence_word, group=self.group)
+
+    def _check_stream(self):
+        """The collectives that order the ranks run on torch's current stream, the library's kernels on the context's
+        stream: the two must be the same stream, or nothing orders a peer's stores against this rank's GEMM."""
+        current = torch.cuda.current_stream(self.device).cuda_stream
+        if (self.ctx.stream or 0) != (current or 0):
+            raise RuntimeError("PeerExpertParallel: the context's stream is not torch's current stream on this device; create the "
+                               "DgContext on the stream the step runs on, or wrap the step in torch.cuda.stream(...)")
 
     def operand(self):
         """The arena as the grouped GEMMs' A: `capacity` rows, of which the group table bounds the work (masked layout: one

@@ -114,8 +114,9 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous_ends(dg_ctx* ctx, const dg_lp_operand* 
  * kernels write if a bounded wait runs out, live in an array that is part of the library image
  * (about 16.3 KB on every GPU that loads the library, held until the process exits).
  *   - num_groups may be at most DG_STATIC_MAX_GROUPS; larger values return DG_ERR_SHAPE.
- *   - The first call on a device looks up the array's device address (once, with that device
- *     current).  Make that first call before any stream capture.
+ *   - The first call on a device looks up the array's device address and opts every kernel this
+ *     path can launch into the large shared-memory carve-out (once, with that device current).
+ *     Make that first call before any stream capture.
  *   - Every call on a device uses the same array, which still holds the previous call's table; the
  *     call clears the entries it needs on `cuda_stream` first.  Two calls whose GPU work can overlap
  *     (different streams, or different threads) race on it: keep them on one stream.
@@ -124,6 +125,12 @@ int dg_m_grouped_fp8_fp4_gemm_contiguous_ends(dg_ctx* ctx, const dg_lp_operand* 
 #define DG_STATIC_MAX_GROUPS 4096
 int dg_m_grouped_fp8_fp4_gemm_contiguous_static(int device, void* cuda_stream, const dg_lp_operand* a, const int32_t* m_indices,
                                                 const dg_lp_operand* b, const dg_out* out, uint32_t num_groups, const dg_epilogue* epi);
+/* No counterpart in the reference.  What dg_ctx_sync is to the context-based calls: waits for `cuda_stream`, then reads
+ * the 16-byte record in the built-in array that a kernel of the call above writes when one of its bounded waits runs
+ * out (the kernel then stops early and leaves the output incomplete).  Returns DG_ERR_TIMEOUT with the block and wait
+ * site and clears the record, or DG_OK.  Allocates nothing.  A host that uses the allocation-free call should poll this
+ * whenever it synchronises: without it such an event goes unnoticed and the record stays set until the process exits. */
+int dg_static_check_status(int device, void* cuda_stream);
 
 /* ops_sm100.rs:815 (m_grouped_fp8_fp4_gemm_masked_dev).  a.rows = m_max (per group), data
  * (num_groups, m_max, k); b.rows = num_groups * n; masked_m (device, int32 per group) is read on
