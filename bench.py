@@ -710,7 +710,7 @@ def dequant_rows(torch, q, sf, idx, k, gran, total_rows):
     words = sf.view(-1, stride)[:, idx].to(torch.int64) & 0xFFFFFFFF            # (cols, rows)
     kb = torch.arange(k // gran, device=q.device)
     exps = (words[kb // 4] >> (8 * (kb % 4)).unsqueeze(1)) & 0xFF                # (k / gran, rows)
-    scale = torch.ldexp(torch.ones((), dtype=torch.float64, device=q.device), (exps - 127).to(torch.int32)).t()
+    scale = torch.pow(2.0, (exps - 127).to(torch.float64)).t()
     return vals * scale.repeat_interleave(gran, dim=1)
 
 
