@@ -177,11 +177,22 @@ uint32_t dg_get_theoretical_mk_alignment_for_contiguous_layout(uint32_t arch_maj
 // Tile choice for 148 SMs / 227 KB shared memory / 512 TMEM columns.  A rows always ride the
 // UMMA M dimension (128 per tile); BLOCK_N is picked from the widths the epilogue of the output
 // type can store, minimising waves x per-tile cost; stages fill the shared memory left over.
-static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out);
-int dg_best_config(const dg_desc* d, dg_config* out) { return choose_config(d, 0, out); }
+// What the launcher needs to know about a choice (the public dg_config describes the same choice in the reference's terms).
+struct KernelPlan {
+    bool swap;                 // weights on the UMMA M dimension, activation rows on UMMA N
+    uint32_t ctas, umma_n, halves, stages, accum, smem;
+    uint32_t splits;           // K ranges summed by a second kernel (first tile family)
+    uint32_t cluster_splits;   // K ranges summed inside a cluster (swapped family)
+    uint32_t tiles;
+};
+static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out, KernelPlan* plan);
+int dg_best_config(const dg_desc* d, dg_config* out) {
+    KernelPlan plan;
+    return choose_config(d, 0, out, &plan);
+}
 
 // no_k_ranges: the caller adds into the output (K ranges would need the sum to be written, not added)
-static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out) {
+static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out, KernelPlan* plan) {
     if (d == nullptr || out == nullptr) return fail(DG_ERR_SHAPE, "null argument");
     if ((d->a_bits != 8 && d->a_bits != 4) || (d->b_bits != 8 && d->b_bits != 4)) return fail(DG_ERR_SHAPE, "operand bits must be 8 or 4");
     // two packed e2m1 operands run on kind::mxf4 (256 elements per 128-byte slab); an e4m3 x e2m1 pair runs on
@@ -281,8 +292,105 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
         }
     }
     }
+    // ---- the swapped family: weight rows on UMMA M, activation rows on UMMA N (bf16 / f32 outputs).  Chosen for dense GEMMs
+    // with at most 256 activation rows, where the first family would leave most of its 128-row tiles empty and, having few
+    // tiles, fill few SMs; DG_SWAP=1 forces it wherever it applies, DG_SWAP=0 forbids it.
+    {
+        const char* force_swap = getenv("DG_SWAP");
+        const bool forced = force_swap && atoi(force_swap) != 0, forbidden = force_swap && atoi(force_swap) == 0;
+        const bool plain_out = d->cd_dtype == DG_OUT_BF16 || d->cd_dtype == DG_OUT_F32;
+        const bool dense = d->gemm_type == DG_GEMM_NORMAL || d->gemm_type == DG_GEMM_BATCHED;
+        const bool want = forced || (d->gemm_type == DG_GEMM_NORMAL && d->m <= 256);
+        if (plain_out && want && !forbidden) {
+            uint32_t s_n = 0, s_ctas = 0, s_halves = 0, s_stages = 0, s_accum = 0, s_split = 1, s_tiles = 0;
+            double s_cost = 0;
+            for (uint32_t halves = 1; halves <= 2; ++halves) {
+                if (force_halves && static_cast<uint32_t>(atoi(force_halves)) != halves) continue;
+                const uint32_t block_k = half_k * halves;
+                // kernel operand A is the caller's b (weights), kernel operand B the caller's a (activation rows)
+                const uint32_t sfa_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
+                const uint32_t sfb_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
+                const uint32_t total_kb = ceil_div(d->k, block_k);
+                for (uint32_t ctas = 1; ctas <= 2; ++ctas) {
+                    if (force_ctas && static_cast<uint32_t>(atoi(force_ctas)) != ctas) continue;
+                    if (ctas == 2 && sms < 2) continue;
+                    const uint32_t step_n = 16 * ctas;
+                    // rows a tile may have: everything a dense problem has (up to 256), else 256 and the tile's UMMA N follows the group
+                    uint32_t bn = dense && d->m <= 256 ? ceil_div(d->m, step_n) * step_n : 256;
+                    if (force_n) bn = static_cast<uint32_t>(atoi(force_n));
+                    if (bn == 0 || bn > 256 || bn % step_n != 0) continue;
+                    const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
+                    if (bn + sf_cols > 512) continue;
+                    const uint32_t accum = 2 * bn + sf_cols <= 512 ? 2 : 1;
+                    const uint32_t a_blocks = ceil_div(d->n, 128 * ctas);
+                    double row_blocks;
+                    if (dense) row_blocks = static_cast<double>(groups) * ceil_div(d->m, bn);
+                    else if (d->gemm_type == DG_GEMM_M_GROUPED_CONTIGUOUS) {
+                        const double per_group = static_cast<double>(d->m) / groups;
+                        row_blocks = groups * ((per_group > align / 2.0 ? per_group - align / 2.0 : per_group) / bn + 0.5);
+                    } else row_blocks = groups * (static_cast<double>(d->expected_m ? d->expected_m : d->m) / bn + 0.5);
+                    const uint32_t tiles = static_cast<uint32_t>(row_blocks * a_blocks + 0.999);
+                    const uint32_t max_split = d->gemm_type == DG_GEMM_NORMAL ? 8 / ctas : 1;
+                    for (uint32_t split = 1; split <= max_split; ++split) {
+                        if (force_splits && static_cast<uint32_t>(atoi(force_splits)) != split) continue;
+                        const uint32_t kb_per = ceil_div(total_kb, split);
+                        if (split > 1 && total_kb < 2 * split) continue;       // at least two k-blocks per range
+                        uint32_t stages = force_stages ? static_cast<uint32_t>(atoi(force_stages)) : dg::kMaxStages;
+                        if (stages > dg::kMaxStages) stages = dg::kMaxStages;
+                        while (stages > 1 && dg::gemm_smem_bytes(bn, ctas, d->cd_dtype, stages, sfa_words, sfb_words, halves, true) > kSmemCapacity) --stages;
+                        if (dg::gemm_smem_bytes(bn, ctas, d->cd_dtype, stages, sfa_words, sfb_words, halves, true) > kSmemCapacity) continue;
+                        if (stages < 3 && !force_stages) continue;
+                        // the exchange buffer of the K ranges lies over the stage buffers
+                        if (split > 1 && dg::gemm_stage_bytes(bn, ctas, stages, halves) < split * ceil_div(bn, split) * 512) continue;
+                        const double bytes_kb = halves * (16384.0 + bn / ctas * 128.0);                  // per CTA and k-block
+                        const double stream = kb_per * bytes_kb / 64.0;
+                        const double mma = kb_per * halves * 4.0 * (bn * 0.5 > 118.0 ? bn * 0.5 : 118.0);
+                        const double per_tile = (stream > mma ? stream : mma) + (split > 1 ? 3500.0 : (accum == 1 ? 12.0 * bn : 2.0 * bn)) + 2500.0;
+                        const double ctas_total = static_cast<double>(tiles) * split * ctas;
+                        const double waves = ctas_total <= sms ? 1.0 : ctas_total / sms;               // the hardware refills SMs as clusters finish
+                        const double hbm = (static_cast<double>(d->n) * groups * d->k * (d->b_bits / 8.0) + static_cast<double>(d->m) * d->k + 2.0 * d->m * d->n) / 3300.0;
+                        const double l2 = ctas_total * kb_per * bytes_kb / 9000.0;
+                        double cost = waves * per_tile;
+                        if (hbm > cost) cost = hbm;
+                        if (l2 > cost) cost = l2;
+                        cost += 0.1 * per_tile + l2 * 0.01;      // among equals: more CTAs in flight, fewer bytes through L2
+                        if (s_n == 0 || cost < s_cost * (1.0 - 1e-9)) {
+                            s_n = bn; s_ctas = ctas; s_halves = halves; s_stages = stages; s_accum = accum; s_split = split; s_tiles = tiles;
+                            s_cost = cost;
+                        }
+                    }
+                }
+            }
+            if (s_n != 0) {
+                const uint32_t block_k = half_k * s_halves;
+                const uint32_t sfa_words = 4 * d->gran_b >= block_k ? 1 : block_k / (4 * d->gran_b);
+                const uint32_t sfb_words = 4 * d->gran_a >= block_k ? 1 : block_k / (4 * d->gran_a);
+                plan->swap = true;
+                plan->ctas = s_ctas; plan->umma_n = s_n; plan->halves = s_halves; plan->stages = s_stages; plan->accum = s_accum;
+                plan->splits = 1; plan->cluster_splits = s_split; plan->tiles = s_tiles;
+                plan->smem = dg::gemm_smem_bytes(s_n, s_ctas, d->cd_dtype, s_stages, sfa_words, sfb_words, s_halves, true);
+                out->swap_ab = 1;
+                out->block_m = s_n;            // activation rows per tile (an upper bound: a tile's UMMA N follows its rows)
+                out->block_n = 128 * s_ctas;   // weight rows per tile
+                out->block_k = block_k;
+                out->cluster_m = 1;
+                out->cluster_n = s_ctas;
+                out->num_stages = s_stages;
+                out->num_accum_stages = s_accum;
+                out->smem_size = plan->smem;
+                out->num_tiles = s_tiles;
+                out->num_splits = s_split;
+                return DG_OK;
+            }
+            if (forced) return fail(DG_ERR_SHAPE, "no tile configuration of the swapped family fits (DG_BLOCK_N=%s DG_CTAS=%s)", force_n ? force_n : "",
+                                    force_ctas ? force_ctas : "");
+        }
+    }
     if (best_n == 0) return fail(DG_ERR_SHAPE, "no tile configuration fits (DG_BLOCK_N=%s DG_CTAS=%s)", force_n ? force_n : "", force_ctas ? force_ctas : "");
     const uint32_t stages = best_stages;
+    plan->swap = false;
+    plan->ctas = best_ctas; plan->umma_n = best_n; plan->halves = best_halves; plan->stages = best_stages; plan->accum = best_accum;
+    plan->splits = best_splits; plan->cluster_splits = 1; plan->tiles = best_tiles;
     out->swap_ab = 0;
     out->block_m = 128 * best_ctas;
     out->block_n = best_n;
@@ -298,6 +406,7 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out)
                                          sfb_words, best_halves);
     out->num_tiles = best_tiles;
     out->num_splits = best_splits;
+    plan->smem = out->smem_size;
     return DG_OK;
 }
 
@@ -372,22 +481,22 @@ cudaError_t launch_reduce(uint32_t blocks, cudaStream_t stream, const float* par
 
 // The opt-in to the full shared-memory carve-out is per kernel instantiation and per device; the first
 // call also makes the runtime load that kernel's image.
-template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
+template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas, bool kSwap = false>
 cudaError_t configure_kernel() {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && (configured.load() & (1ull << dev))) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(dg::dg_gemm_kernel<kFmt, kOut, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(dg::dg_gemm_kernel<kFmt, kOut, kCtas, kSwap>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(kSmemCapacity));
     if (e == cudaSuccess && dev < 64) configured.fetch_or(1ull << dev);
     return e;
 }
 
-template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
+template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas, bool kSwap = false>
 cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
-    auto kernel = dg::dg_gemm_kernel<kFmt, kOut, kCtas>;
-    cudaError_t e = configure_kernel<kFmt, kOut, kCtas>();
+    auto kernel = dg::dg_gemm_kernel<kFmt, kOut, kCtas, kSwap>;
+    cudaError_t e = configure_kernel<kFmt, kOut, kCtas, kSwap>();
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -397,7 +506,7 @@ cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem,
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = kCtas;
+    attr[0].val.clusterDim.x = kCtas * (kSwap ? p.cluster_splits : 1u);   // swapped family: the K ranges of a tile share a cluster
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     // the kernel waits for its predecessor itself (griddep_wait) after its set-up: let the two overlap
@@ -406,6 +515,13 @@ cudaError_t launch_kernel(const dg::GemmParams& p, uint32_t grid, uint32_t smem,
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, kernel, p, maps[0], maps[1], maps[2], maps[3], maps[4]);
+}
+
+template <uint32_t kFmt, uint32_t kCtas>
+cudaError_t launch_swapped(int kind, const dg::GemmParams& p, uint32_t grid, uint32_t smem, cudaStream_t stream, const CUtensorMap* maps) {
+    if (kind == DG_OUT_BF16) return launch_kernel<kFmt, dg::kOutBf16, kCtas, true>(p, grid, smem, stream, maps);
+    if (kind == DG_OUT_F32) return launch_kernel<kFmt, dg::kOutF32, kCtas, true>(p, grid, smem, stream, maps);
+    return cudaErrorInvalidValue;
 }
 
 template <uint32_t kFmt, uint32_t kCtas>
@@ -426,6 +542,10 @@ cudaError_t configure_contiguous_kernels_of() {
     if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutBf16, 2>();
     if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutF32, 1>();
     if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutF32, 2>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutBf16, 1, true>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutBf16, 2, true>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutF32, 1, true>();
+    if (e == cudaSuccess) e = configure_kernel<kFmt, dg::kOutF32, 2, true>();
     return e;
 }
 // Everything dg_m_grouped_fp8_fp4_gemm_contiguous[_ends] can launch, configured (and loaded) for the current device.
@@ -481,17 +601,24 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     dg_desc desc = {pr.type, pr.m, pr.n, pr.k, pr.groups, pr.expected_m, a->bits, b->bits, a->gran_k, b->gran_k,
                     static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms)};
     dg_config cfg;
-    rc = choose_config(&desc, e.accumulate ? 1u : 0u, &cfg);
+    KernelPlan plan;
+    rc = choose_config(&desc, e.accumulate ? 1u : 0u, &cfg, &plan);
     if (rc) return rc;
+    const bool swap = plan.swap;
+    // the swapped family runs the same kernel with the operands' roles exchanged: its operand A (UMMA M side) is the weights
+    const dg_lp_operand* ka = swap ? b : a;
+    const dg_lp_operand* kb = swap ? a : b;
+    const uint32_t ka_rows = swap ? pr.n : pr.m, kb_rows = swap ? pr.m : pr.n;              // per group
+    const uint32_t ka_groups = swap ? b_groups : a_groups, kb_groups = swap ? a_groups : b_groups;
     static const bool print_cfg = [] { const char* v = getenv("DG_PRINT_CONFIGS"); return v && strcmp(v, "0") != 0; }();
     if (print_cfg)
-        fprintf(stderr, "[dgb200] type=%u m=%u n=%u k=%u groups=%u -> block=%ux%ux%u ctas=%u stages=%u accum=%u smem=%u tiles~%u\n", pr.type, pr.m,
-                pr.n, pr.k, pr.groups, cfg.block_m, cfg.block_n, cfg.block_k, cfg.cluster_m, cfg.num_stages, cfg.num_accum_stages, cfg.smem_size,
-                cfg.num_tiles);
+        fprintf(stderr, "[dgb200] type=%u m=%u n=%u k=%u groups=%u -> swap_ab=%u block=%ux%ux%u ctas=%u stages=%u accum=%u smem=%u tiles~%u splits=%u\n",
+                pr.type, pr.m, pr.n, pr.k, pr.groups, cfg.swap_ab, cfg.block_m, cfg.block_n, cfg.block_k, plan.ctas, cfg.num_stages,
+                cfg.num_accum_stages, cfg.smem_size, cfg.num_tiles, cfg.num_splits);
 
     const bool mxf4 = a->bits == 4 && b->bits == 4;
     const uint32_t block_k = cfg.block_k;
-    const uint32_t splits = cfg.num_splits;
+    const uint32_t splits = plan.splits;
     const uint32_t ws_pitch = align4(pr.n);
     if (splits > 1) {
         const size_t need = static_cast<size_t>(splits) * pr.m * ws_pitch;
@@ -502,9 +629,9 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
             ctx->splitk_ws_cap = need;
         }
     }
-    const uint32_t sfa_words = 4 * a->gran_k >= block_k ? 1 : block_k / (4 * a->gran_k);
-    const uint32_t sfb_words = 4 * b->gran_k >= block_k ? 1 : block_k / (4 * b->gran_k);
-    const uint32_t sf_block_n = ceil_div(cfg.block_n, 128) * 128;
+    const uint32_t sfa_words = 4 * ka->gran_k >= block_k ? 1 : block_k / (4 * ka->gran_k);
+    const uint32_t sfb_words = 4 * kb->gran_k >= block_k ? 1 : block_k / (4 * kb->gran_k);
+    const uint32_t sf_block_n = ceil_div(plan.umma_n, 128) * 128;
 
     CUtensorMap maps[5];
     {
@@ -513,31 +640,31 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         auto map_dtype = [&](uint32_t bits) {
             return bits == 8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (mxf4 ? CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B);
         };
-        const uint64_t a_pitch = a->bits == 4 ? a->ld / 2 : a->ld, b_pitch = b->bits == 4 ? b->ld / 2 : b->ld;
-        uint64_t dims[3] = {pr.k, pr.m, a_groups};
-        uint64_t strides[2] = {a_pitch, a_pitch * pr.m};
+        const uint64_t a_pitch = ka->bits == 4 ? ka->ld / 2 : ka->ld, b_pitch = kb->bits == 4 ? kb->ld / 2 : kb->ld;
+        uint64_t dims[3] = {pr.k, ka_rows, ka_groups};
+        uint64_t strides[2] = {a_pitch, a_pitch * ka_rows};
         const uint32_t slab = mxf4 ? 256u : 128u;    // one 128-byte slab of K per TMA box
         uint32_t box[3] = {slab, dg::kBlockM, 1};
-        rc = encode_map(&maps[0], map_dtype(a->bits), 3, a->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
+        rc = encode_map(&maps[0], map_dtype(ka->bits), 3, ka->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
         if (rc) return rc;
-        uint64_t bdims[3] = {pr.k, pr.n, b_groups};
-        uint64_t bstrides[2] = {b_pitch, b_pitch * pr.n};
-        uint32_t bbox[3] = {slab, cfg.block_n / cfg.cluster_m, 1};
-        rc = encode_map(&maps[1], map_dtype(b->bits), 3, b->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
+        uint64_t bdims[3] = {pr.k, kb_rows, kb_groups};
+        uint64_t bstrides[2] = {b_pitch, b_pitch * kb_rows};
+        uint32_t bbox[3] = {slab, plan.umma_n / plan.ctas, 1};
+        rc = encode_map(&maps[1], map_dtype(kb->bits), 3, kb->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
         if (rc) return rc;
     }
-    const uint32_t sfa_cols = dg_sf_packed_cols(pr.k, a->gran_k), sfb_cols = dg_sf_packed_cols(pr.k, b->gran_k);
+    const uint32_t sfa_cols = dg_sf_packed_cols(pr.k, ka->gran_k), sfb_cols = dg_sf_packed_cols(pr.k, kb->gran_k);
     {
         // bf16 operands carry no scales: the kernel never issues these loads, the maps only have to be well-formed
-        uint64_t dims[2] = {align4(pr.m), static_cast<uint64_t>(sfa_cols) * a_groups};
-        uint64_t strides[1] = {static_cast<uint64_t>(align4(pr.m)) * 4};
+        uint64_t dims[2] = {align4(ka_rows), static_cast<uint64_t>(sfa_cols) * ka_groups};
+        uint64_t strides[1] = {static_cast<uint64_t>(align4(ka_rows)) * 4};
         uint32_t box[2] = {128, sfa_words};
-        rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? a->data : a->sf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA");
+        rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? ka->data : ka->sf, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA");
         if (rc) return rc;
-        uint64_t bdims[2] = {align4(pr.n), static_cast<uint64_t>(sfb_cols) * b_groups};
-        uint64_t bstrides[1] = {static_cast<uint64_t>(align4(pr.n)) * 4};
-        uint32_t bbox[2] = {swiglu ? cfg.block_n / 2 : sf_block_n, sfb_words};   // fused activation: gate rows and up rows as two boxes
-        rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? b->data : b->sf, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB");
+        uint64_t bdims[2] = {align4(kb_rows), static_cast<uint64_t>(sfb_cols) * kb_groups};
+        uint64_t bstrides[1] = {static_cast<uint64_t>(align4(kb_rows)) * 4};
+        uint32_t bbox[2] = {swiglu ? plan.umma_n / 2 : sf_block_n, sfb_words};   // fused activation: gate rows and up rows as two boxes
+        rc = encode_map(&maps[3], CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, pr.bf16 ? kb->data : kb->sf, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB");
         if (rc) return rc;
     }
     {
@@ -563,26 +690,28 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
 
     dg::GemmParams p;
     memset(&p, 0, sizeof(p));
-    p.m = pr.m;
-    p.n = n_out;
+    p.m = swap ? pr.n : pr.m;     // rows of the kernel's operand A per group (swapped family: weight rows)
+    p.n = swap ? pr.m : n_out;
     p.k = pr.k;
-    p.tile_n = swiglu ? cfg.block_n / 2 : cfg.block_n;
+    p.tile_n = swiglu ? plan.umma_n / 2 : plan.umma_n;
     p.num_groups = pr.groups;
     p.gemm_type = pr.type;
-    p.block_n = cfg.block_n;
+    p.block_n = plan.umma_n;
     p.block_k_elems = block_k;
     p.num_splits = splits;
-    p.kb_per_split = splits > 1 ? ceil_div(ceil_div(ceil_div(pr.k, block_k), splits), 4) * 4 : ceil_div(pr.k, block_k);
-    p.num_stages = cfg.num_stages;
-    p.num_accum_stages = cfg.num_accum_stages;
-    p.gran_a = a->gran_k;
-    p.gran_b = b->gran_k;
+    p.cluster_splits = plan.cluster_splits;
+    p.kb_per_split = splits > 1 ? ceil_div(ceil_div(ceil_div(pr.k, block_k), splits), 4) * 4 : ceil_div(ceil_div(pr.k, block_k), plan.cluster_splits);
+    p.out_group_rows = (pr.type == DG_GEMM_M_GROUPED_MASKED || pr.type == DG_GEMM_BATCHED) ? pr.m : 0;
+    p.num_stages = plan.stages;
+    p.num_accum_stages = plan.accum;
+    p.gran_a = ka->gran_k;
+    p.gran_b = kb->gran_k;
     // measured on B200: a 16U4_ALIGN16B load (e2m1 expanded to one code per byte) fills 128 bytes of shared memory per
     // 128 elements but signals only the 64 packed bytes it read on its barrier
-    p.tx_shift_a = (!mxf4 && a->bits == 4) ? 1 : 0;
-    p.tx_shift_b = (!mxf4 && b->bits == 4) ? 1 : 0;
-    p.fmt_a = a->bits == 8 ? 0u : 5u;
-    p.fmt_b = b->bits == 8 ? 0u : 5u;
+    p.tx_shift_a = (!mxf4 && ka->bits == 4) ? 1 : 0;
+    p.tx_shift_b = (!mxf4 && kb->bits == 4) ? 1 : 0;
+    p.fmt_a = ka->bits == 8 ? 0u : 5u;
+    p.fmt_b = kb->bits == 8 ? 0u : 5u;
     p.sf_a_cols = sfa_cols;
     p.sf_b_cols = sfb_cols;
     p.mk_alignment = align;
@@ -592,7 +721,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.out_ptr = out->buf;
     p.out_ld = out->ld;
     p.accumulate = e.accumulate ? 1 : 0;
-    p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges alpha is applied to the sum
+    p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges summed by the second kernel alpha is applied there
     p.alpha = e.alpha;
     p.sfd = out->sfd;
     p.sfd_stride = align4(pr.m);
@@ -607,19 +736,29 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     }
 #endif
 
-    const uint32_t ctas = cfg.cluster_m;
+    const uint32_t ctas = plan.ctas;
     uint32_t grid = static_cast<uint32_t>(ctx->num_sms) / ctas * ctas;
     if (pr.type == DG_GEMM_NORMAL || pr.type == DG_GEMM_BATCHED)
-        grid = cfg.num_tiles * splits * ctas < grid ? cfg.num_tiles * splits * ctas : grid;
+        grid = plan.tiles * splits * ctas < grid ? plan.tiles * splits * ctas : grid;
+    // K ranges summed inside a cluster: one cluster per output tile, as many clusters as tiles
+    if (swap && plan.cluster_splits > 1) grid = plan.tiles * plan.cluster_splits * ctas;
     const int kernel_out = splits > 1 ? DG_OUT_F32 : out->kind;
+    const uint32_t smem = plan.smem;
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     cudaError_t ce;
-    if (pr.bf16) ce = ctas == 2 ? launch_by_out<dg::kFmtBf16, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
-                                : launch_by_out<dg::kFmtBf16, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
-    else if (mxf4) ce = ctas == 2 ? launch_by_out<dg::kFmtMxf4, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
-                                  : launch_by_out<dg::kFmtMxf4, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
-    else ce = ctas == 2 ? launch_by_out<dg::kFmtMxf8f6f4, 2>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps)
-                        : launch_by_out<dg::kFmtMxf8f6f4, 1>(kernel_out, p, grid, cfg.smem_size, ctx->stream, maps);
+    if (swap) {
+        if (pr.bf16) ce = ctas == 2 ? launch_swapped<dg::kFmtBf16, 2>(kernel_out, p, grid, smem, ctx->stream, maps)
+                                    : launch_swapped<dg::kFmtBf16, 1>(kernel_out, p, grid, smem, ctx->stream, maps);
+        else if (mxf4) ce = ctas == 2 ? launch_swapped<dg::kFmtMxf4, 2>(kernel_out, p, grid, smem, ctx->stream, maps)
+                                      : launch_swapped<dg::kFmtMxf4, 1>(kernel_out, p, grid, smem, ctx->stream, maps);
+        else ce = ctas == 2 ? launch_swapped<dg::kFmtMxf8f6f4, 2>(kernel_out, p, grid, smem, ctx->stream, maps)
+                            : launch_swapped<dg::kFmtMxf8f6f4, 1>(kernel_out, p, grid, smem, ctx->stream, maps);
+    } else if (pr.bf16) ce = ctas == 2 ? launch_by_out<dg::kFmtBf16, 2>(kernel_out, p, grid, smem, ctx->stream, maps)
+                                : launch_by_out<dg::kFmtBf16, 1>(kernel_out, p, grid, smem, ctx->stream, maps);
+    else if (mxf4) ce = ctas == 2 ? launch_by_out<dg::kFmtMxf4, 2>(kernel_out, p, grid, smem, ctx->stream, maps)
+                                  : launch_by_out<dg::kFmtMxf4, 1>(kernel_out, p, grid, smem, ctx->stream, maps);
+    else ce = ctas == 2 ? launch_by_out<dg::kFmtMxf8f6f4, 2>(kernel_out, p, grid, smem, ctx->stream, maps)
+                        : launch_by_out<dg::kFmtMxf8f6f4, 1>(kernel_out, p, grid, smem, ctx->stream, maps);
     if (ce == cudaSuccess && splits > 1) {
         const uint64_t threads = static_cast<uint64_t>(pr.m) * ceil_div(pr.n, 4);
         const uint32_t blocks = static_cast<uint32_t>((threads + 255) / 256);

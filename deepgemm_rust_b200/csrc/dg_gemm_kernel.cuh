@@ -22,6 +22,18 @@
 // CTA's TMEM receives its own 128 accumulator rows and runs its own epilogue.
 // Accumulators are double-buffered in TMEM whenever 2*BLOCK_N plus the scale columns fit
 // in 512 columns, so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// kSwap = true is the second tile family, for few activation rows per weight matrix (skinny dense
+// GEMMs, small expert groups): the WEIGHT rows ride the UMMA M dimension (128 per CTA, 256 per
+// pair) and the activation rows the UMMA N dimension, whose width follows the rows a tile really
+// has (a multiple of 16, up to BLOCK_N).  The host hands the operands over with their roles
+// exchanged, so loads, scale path and UMMA issue are the code above; what differs is the tile
+// walk and the epilogue, which holds D transposed (lane = output column, TMEM column = output
+// row) and writes it with plain stores, 32 consecutive columns of one output row per warp.
+// Dense GEMMs with few tiles also cut K into ranges, one per CTA (or pair) of a cluster; the
+// partial tiles are exchanged through distributed shared memory (every CTA sums a slice of the
+// tile's rows over all ranges, in range order) and each CTA stores its slice: one launch, no
+// workspace, a deterministic sum.
 #pragma once
 #include "dg_ptx.cuh"
 #include "dg_activation.cuh"
@@ -69,6 +81,8 @@ struct GemmParams {
     uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
     float alpha;
     uint32_t sfd_stride;       // output scale words: stride between word columns (fp8 output)
+    uint32_t cluster_splits;   // kSwap, dense: K ranges handled by the CTAs (pairs) of one cluster and summed through shared memory
+    uint32_t out_group_rows;   // kSwap: output rows between two groups' outputs (masked / batched layouts)
     const uint32_t* grouped_layout;  // contiguous: end row of each group; masked: valid rows per group
     uint32_t* sfd;
     Status* status;
@@ -89,22 +103,29 @@ struct GemmParams {
 struct Tile {
     uint32_t m0, n0;     // first row / column of the tile (row is group-local except in the contiguous arena)
     uint32_t m_end;      // rows at or beyond this one belong to someone else (next group / out of range): never stored
+    uint32_t n_end;      // kSwap: rows of the N-side operand at or beyond this one are not part of the tile (group end / matrix end)
     uint32_t ga, gb;     // group coordinate of A/SFA and of B/SFB
     uint32_t gd;         // third coordinate of D: the group, or the K range when K is split
     uint32_t kb0, kb1;   // k-block range of this tile
 };
 
 // Walks the tile list of one CTA.  Every role runs its own copy and sees the same sequence.
+// In the swapped family "m" is the weight dimension (rows of the UMMA M side, per group) and "n" the
+// activation rows (UMMA N side): p.m / num_m_blocks count weight rows, groups are ranges of N-side rows.
 struct Scheduler {
     const GemmParams& p;
-    uint32_t tile_m, worker, num_workers;   // rows per tile; CTA (or CTA pair) index and count
+    bool swap;
+    uint32_t tile_m, worker, num_workers, split;   // rows per tile; cluster index and count; K range of this CTA (pair)
     uint32_t num_m_blocks, num_n_blocks, iter;
     uint32_t cur_group, cum_begin, cur_m_blocks, cur_row_start, cur_row_end;
 
-    DG_DEVICE Scheduler(const GemmParams& params, uint32_t ctas) : p(params) {
+    DG_DEVICE Scheduler(const GemmParams& params, uint32_t ctas, bool swapped = false, uint32_t cluster_rank = 0) : p(params) {
+        swap = swapped;
         tile_m = kBlockM * ctas;
-        worker = blockIdx.x / ctas;
-        num_workers = gridDim.x / ctas;
+        const uint32_t per_cluster = ctas * (swap ? p.cluster_splits : 1u);
+        worker = blockIdx.x / per_cluster;
+        num_workers = gridDim.x / per_cluster;
+        split = swap ? cluster_rank / ctas : 0u;
         num_m_blocks = (p.m + tile_m - 1) / tile_m;
         num_n_blocks = (p.n + p.tile_n - 1) / p.tile_n;
         iter = 0;
@@ -112,25 +133,27 @@ struct Scheduler {
         cum_begin = 0;
         cur_m_blocks = 0;
         cur_row_start = 0;
-        cur_row_end = p.m;
+        cur_row_end = swap ? p.n : p.m;
         if (p.gemm_type == kGemmContiguous || p.gemm_type == kGemmMasked) load_group();
     }
 
+    // rows of the current group, and how many row blocks they make (of tile_m rows, or of block_n rows when swapped)
     DG_DEVICE void load_group() {
         if (cur_group >= p.num_groups) return;
+        const uint32_t limit = swap ? p.n : p.m, block = swap ? p.block_n : tile_m;
         if (p.gemm_type == kGemmContiguous) {
             const uint32_t prev_end = cur_group == 0 ? 0u : __ldg(p.grouped_layout + cur_group - 1);
             const uint32_t end = __ldg(p.grouped_layout + cur_group);
             cur_row_start = (prev_end + p.mk_alignment - 1) / p.mk_alignment * p.mk_alignment;
             const uint32_t rows = end > cur_row_start ? end - cur_row_start : 0u;
-            cur_row_end = end < p.m ? end : p.m;
-            cur_m_blocks = (rows + tile_m - 1) / tile_m;
+            cur_row_end = end < limit ? end : limit;
+            cur_m_blocks = (rows + block - 1) / block;
         } else {
             const int32_t valid = static_cast<int32_t>(__ldg(p.grouped_layout + cur_group));
-            const uint32_t rows = valid <= 0 ? 0u : (static_cast<uint32_t>(valid) < p.m ? static_cast<uint32_t>(valid) : p.m);
+            const uint32_t rows = valid <= 0 ? 0u : (static_cast<uint32_t>(valid) < limit ? static_cast<uint32_t>(valid) : limit);
             cur_row_start = 0;
             cur_row_end = rows;      // nothing is stored (and a pair's second CTA loads nothing) past the group's valid rows
-            cur_m_blocks = (rows + tile_m - 1) / tile_m;
+            cur_m_blocks = (rows + block - 1) / block;
         }
     }
 
@@ -139,15 +162,51 @@ struct Scheduler {
         const uint32_t total_kb = (p.k + p.block_k_elems - 1) / p.block_k_elems;
         t.kb0 = 0;
         t.kb1 = total_kb;
+        t.n_end = p.n;
+        if (swap) {
+            if (p.cluster_splits > 1) {
+                // k-blocks dealt out evenly: no range is empty as long as there are at least as many k-blocks as ranges
+                t.kb0 = split * total_kb / p.cluster_splits;
+                t.kb1 = (split + 1) * total_kb / p.cluster_splits;
+            }
+            t.m_end = p.m;
+            if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmBatched) {
+                const uint32_t per_group = num_m_blocks * num_n_blocks;
+                if (idx >= per_group * p.num_groups) return false;
+                const uint32_t g = idx / per_group, r = idx - g * per_group;
+                const uint32_t nb = r / num_m_blocks, mb = r - nb * num_m_blocks;     // weight blocks fastest: CTAs in flight share the rows
+                t.m0 = mb * tile_m;
+                t.n0 = nb * p.block_n;
+                t.ga = t.gb = t.gd = g;
+                return true;
+            }
+            while (true) {
+                if (cur_group >= p.num_groups) return false;
+                const uint32_t end = cum_begin + cur_m_blocks * num_m_blocks;
+                if (idx < end) break;
+                cum_begin = end;
+                ++cur_group;
+                load_group();
+            }
+            const uint32_t in_group = idx - cum_begin;
+            const uint32_t nb = in_group / num_m_blocks, mb = in_group - nb * num_m_blocks;
+            t.m0 = mb * tile_m;
+            t.n0 = cur_row_start + nb * p.block_n;
+            t.n_end = cur_row_end;
+            t.ga = cur_group;
+            t.gb = p.gemm_type == kGemmContiguous ? 0u : cur_group;
+            t.gd = t.gb;
+            return true;
+        }
         if (p.gemm_type == kGemmNormal || p.gemm_type == kGemmBatched) {
             const uint32_t per_group = num_m_blocks * num_n_blocks;
-            uint32_t split = 0;
+            uint32_t split_k = 0;
             if (p.num_splits > 1) {
                 // K ranges of one output tile sit next to each other in the tile order
                 if (idx >= per_group * p.num_splits) return false;
-                split = idx % p.num_splits;
+                split_k = idx % p.num_splits;
                 idx /= p.num_splits;
-                t.kb0 = split * p.kb_per_split;
+                t.kb0 = split_k * p.kb_per_split;
                 t.kb1 = t.kb0 + p.kb_per_split < total_kb ? t.kb0 + p.kb_per_split : total_kb;
             } else if (idx >= per_group * p.num_groups) {
                 return false;
@@ -166,7 +225,7 @@ struct Scheduler {
             t.m_end = p.m;
             t.n0 = nb * p.tile_n;
             t.ga = t.gb = g;
-            t.gd = p.num_splits > 1 ? split : g;
+            t.gd = p.num_splits > 1 ? split_k : g;
             return true;
         }
         while (true) {
@@ -187,6 +246,16 @@ struct Scheduler {
         t.gd = t.ga;
         return true;
     }
+
+    // UMMA N of a tile: the whole BLOCK_N, or in the swapped family the rows the tile really has, rounded up to what
+    // the instruction (and, for a pair, the split of the rows between the two CTAs) allows
+    DG_DEVICE uint32_t umma_n(const Tile& t, uint32_t ctas) const {
+        if (!swap) return p.block_n;
+        const uint32_t rows = t.n_end > t.n0 ? t.n_end - t.n0 : 0u;
+        const uint32_t step = 16 * ctas;
+        const uint32_t n = (rows + step - 1) / step * step;
+        return n < p.block_n ? (n == 0 ? step : n) : p.block_n;
+    }
 };
 
 // How often a scale word must be (re)loaded and how many words one k-block needs.
@@ -203,9 +272,24 @@ DG_DEVICE SfPlan sf_plan(uint32_t gran, uint32_t block_k_elems) {
     return s;
 }
 
+// One output element of the swapped family: alpha, optional accumulation into what the output holds, rounding.
+template <uint32_t kOut>
+DG_DEVICE void store_output(uint8_t* dst, float x, const GemmParams& p) {
+    if (p.has_alpha) x *= p.alpha;
+    if constexpr (kOut == kOutBf16) {
+        uint16_t* d = reinterpret_cast<uint16_t*>(dst);
+        // like the reduce-add store of the other family: the product is rounded to bf16, added to the bf16 addend, rounded again
+        if (p.accumulate) x = __uint_as_float((pack_bf16x2(x, 0.0f) & 0xFFFFu) << 16) + __uint_as_float(static_cast<uint32_t>(*d) << 16);
+        *d = static_cast<uint16_t>(pack_bf16x2(x, 0.0f) & 0xFFFFu);
+    } else {
+        float* d = reinterpret_cast<float*>(dst);
+        *d = p.accumulate ? *d + x : x;
+    }
+}
+
 // kFmt: kFmtMxf8f6f4 (e4m3 / expanded e2m1 operands, block-scaled), kFmtMxf4 (packed e2m1, block-scaled) or
 // kFmtBf16 (bf16 operands seen as K-major rows of 2k bytes, kind::f16, no scale factors: bf16_gemm_sm100.rs).
-template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas>
+template <uint32_t kFmt, uint32_t kOut, uint32_t kCtas, bool kSwap = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -216,14 +300,17 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     constexpr uint32_t kHalfElems = kMXF4 ? 256 : 128;
     const uint32_t kBlockKElems = p.block_k_elems;
     const uint32_t halves = kBlockKElems / kHalfElems;
-    constexpr uint32_t kEpiBufBytes = epilogue_buf_bytes(kOut);
+    constexpr uint32_t kEpiBufBytes = kSwap ? 0u : epilogue_buf_bytes(kOut);   // the swapped family stores from registers
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     // CTA pair: rank 0 issues the UMMAs for both, each CTA owns 128 rows of the 256-row tile
     // and loads half of the B tile
-    const uint32_t cta_rank = kCtas == 2 ? cluster_cta_rank() : 0u;
+    // (a cluster may hold several pairs: the K ranges of one tile in the swapped family; a pair is ranks 2i and 2i + 1)
+    const uint32_t cluster_rank = (kCtas == 2 || kSwap) ? cluster_cta_rank() : 0u;
+    const uint32_t cta_rank = kCtas == 2 ? (cluster_rank & 1u) : 0u;
+    const uint32_t leader_rank = cluster_rank & ~1u;       // kCtas == 2: the CTA of this pair that issues the UMMAs
     const uint32_t block_n = p.block_n;
     const uint32_t load_n = block_n / kCtas;
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
@@ -273,7 +360,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         tmem_relinquish<kCtas>();
     }
     tc_fence_before();
-    if constexpr (kCtas == 2) cluster_sync(); else __syncthreads();
+    if constexpr (kCtas == 2 || kSwap) cluster_sync(); else __syncthreads();
     tc_fence_after();
     // up to here nothing read or wrote global memory: the set-up above may overlap the previous kernel of the stream
     griddep_wait();
@@ -288,19 +375,22 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     // instruction (which alone costs ~190 cycles per UMMA).
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
-        Scheduler sched(p, kCtas);
+        Scheduler sched(p, kCtas, kSwap, cluster_rank);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        const uint32_t full_bar_leader = kCtas == 2 ? mapa_u32(smem_u32(bar_full), 0) : 0u;
+        const uint32_t full_bar_leader = kCtas == 2 ? mapa_u32(smem_u32(bar_full), leader_rank) : 0u;
         while (ok && sched.next(t)) {
             const int32_t row_a = static_cast<int32_t>(t.m0 + cta_rank * kBlockM);
             // fused gate/up activation: rank 0 takes the gate rows [n0, n0 + load_n) of the group's B block, rank 1 the up rows
-            // of the same range, which start p.n rows further down
-            const int32_t row_b = static_cast<int32_t>(kOut == kOutSwiGluFp8 ? t.n0 + cta_rank * p.n : t.n0 + cta_rank * load_n);
+            // of the same range, which start p.n rows further down.  Swapped family: the UMMA takes the first half of its N
+            // rows from rank 0 and the second half from rank 1, so rank 1's box starts where that half starts.
+            const int32_t row_b = static_cast<int32_t>(kOut == kOutSwiGluFp8 ? t.n0 + cta_rank * p.n
+                                                       : (kSwap ? t.n0 + cta_rank * (sched.umma_n(t, kCtas) / 2) : t.n0 + cta_rank * load_n));
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
-                bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
+                // a scale word is loaded where it starts and, for a K range that begins inside a word, at the range's first k-block
+                bool need_a = kScaled && (kb % plan_a.period == 0 || kb == t.kb0), need_b = kScaled && (kb % plan_b.period == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -349,11 +439,9 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     } else if (warp == 1) {
         // ------------------------------------------------------------- UMMA issuer
         if (cta_rank == 0) {
-            Scheduler sched(p, kCtas);
+            Scheduler sched(p, kCtas, kSwap, cluster_rank);
             Tile t;
             uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0;
-            const uint32_t idesc = kScaled ? make_idesc_block_scaled(kBlockM * kCtas, block_n, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b)
-                                           : make_idesc_bf16(kBlockM * kCtas, block_n);
             const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
 #ifdef DG_PROFILE
@@ -368,8 +456,11 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 DG_PROF_ADD(4, t_acc);
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + e * block_n;
+                const uint32_t n_tile = sched.umma_n(t, kCtas);
+                const uint32_t idesc = kScaled ? make_idesc_block_scaled(kBlockM * kCtas, n_tile, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b)
+                                               : make_idesc_bf16(kBlockM * kCtas, n_tile);
                 for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                    bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
+                    bool need_a = kScaled && (kb % plan_a.period == 0 || kb == t.kb0), need_b = kScaled && (kb % plan_b.period == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                     if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -432,8 +523,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                             umma_commit(bar_empty + stage);
                             if (last) umma_commit(bar_tmem_full + e);
                         } else {
-                            umma_commit_2cta(bar_empty + stage, 3);
-                            if (last) umma_commit_2cta(bar_tmem_full + e, 3);
+                            umma_commit_2cta(bar_empty + stage, static_cast<uint16_t>(3u << leader_rank));
+                            if (last) umma_commit_2cta(bar_tmem_full + e, static_cast<uint16_t>(3u << leader_rank));
                         }
                     }
                     __syncwarp();
@@ -450,13 +541,13 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         __syncwarp();
     } else if (warp == 2) {
         // -------------------------------------------------- scale-factor re-ordering
-        Scheduler sched(p, kCtas);
+        Scheduler sched(p, kCtas, kSwap, cluster_rank);
         Tile t;
         uint32_t stage = 0, sf_phase_bits = 0;
         bool ok = true;
         while (ok && sched.next(t)) {
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                bool need_a = kScaled && kb % plan_a.period == 0, need_b = kScaled && kb % plan_b.period == 0;
+                bool need_a = kScaled && (kb % plan_a.period == 0 || kb == t.kb0), need_b = kScaled && (kb % plan_b.period == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -477,7 +568,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     __syncwarp();
                     if (lane == 0) {
                         if constexpr (kCtas == 1) mbar_arrive(bar_sf_ready + stage);
-                        else mbar_arrive_remote(bar_sf_ready + stage, 0);
+                        else mbar_arrive_remote(bar_sf_ready + stage, leader_rank);
                     }
                 }
                 if (++stage == num_stages) stage = 0;
@@ -485,6 +576,69 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         }
         __syncwarp();
     } else if (warp >= 4) {
+      if constexpr (kSwap) {
+        // ------------------------------------------------- epilogue of the swapped family
+        // The accumulator holds D transposed: TMEM lane = output column (a weight row), TMEM column = output row.  For one
+        // output row the 32 lanes of a warp hold 32 consecutive columns, so every store instruction of a warp writes one
+        // 64-byte (bf16) or 128-byte (f32) run of a row; rows past the tile's last valid row are skipped.
+        static_assert(kOut == kOutBf16 || kOut == kOutF32, "the swapped tile family writes bf16 or f32");
+        const uint32_t ew = warp - 4;
+        Scheduler sched(p, kCtas, true, cluster_rank);
+        Tile t;
+        uint32_t it = 0;
+        if (p.cluster_splits > 1) {
+            // K ranges: the partial sums stay in TMEM until every CTA of the cluster has finished its range (after the roles)
+            if (sched.next(t)) mbar_wait(bar_tmem_full, 0, abort_flag, p.status, 0x600);
+        } else {
+            while (sched.next(t)) {
+                const uint32_t e = it % p.num_accum_stages, acc_phase = (it / p.num_accum_stages) & 1;
+                ++it;
+                if (!mbar_wait(bar_tmem_full + e, acc_phase, abort_flag, p.status, 0x600 + e)) break;
+                tc_fence_after();
+                const uint32_t n_tile = sched.umma_n(t, kCtas);
+                const uint32_t rows_left = t.n_end > t.n0 ? t.n_end - t.n0 : 0u;
+                const uint32_t valid = rows_left < n_tile ? rows_left : n_tile;
+                const uint32_t taddr = tmem_base + ((ew * 32) << 16) + e * block_n;
+                const uint32_t col_out = t.m0 + cta_rank * kBlockM + ew * 32 + lane;
+                const bool col_ok = col_out < t.m_end;
+                constexpr uint32_t kElem = kOut == kOutBf16 ? 2 : 4;
+                uint8_t* base = static_cast<uint8_t*>(p.out_ptr) +
+                                ((static_cast<size_t>(t.gd) * p.out_group_rows + t.n0) * p.out_ld + col_out) * kElem;
+                const size_t row_pitch = static_cast<size_t>(p.out_ld) * kElem;
+                auto release_accumulator = [&]() {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
+                        else mbar_arrive_remote(bar_tmem_empty + e, leader_rank);
+                    }
+                };
+                auto store_rows = [&](uint32_t (&v)[32], uint32_t s) {
+                    #pragma unroll
+                    for (uint32_t c = 0; c < 32; ++c) {
+                        const uint32_t row = s * 32 + c;
+                        if (row < valid && col_ok) store_output<kOut>(base + row * row_pitch, __uint_as_float(v[c]), p);
+                    }
+                };
+                const uint32_t chunks = (n_tile + 31) / 32;
+                uint32_t va[32], vb[32];
+                tmem_ld_32x32b_x32(taddr, va);
+                for (uint32_t s = 0; s < chunks; s += 2) {
+                    tmem_ld_wait_x32(va);
+                    const bool has_b = s + 1 < chunks;
+                    if (has_b) tmem_ld_32x32b_x32(taddr + (s + 1) * 32, vb);
+                    else release_accumulator();
+                    store_rows(va, s);
+                    if (has_b) {
+                        tmem_ld_wait_x32(vb);
+                        if (s + 2 < chunks) tmem_ld_32x32b_x32(taddr + (s + 2) * 32, va);
+                        else release_accumulator();
+                        store_rows(vb, s + 1);
+                    }
+                }
+            }
+        }
+      } else {
         // ------------------------------------------------------------------ epilogue
         // 32 accumulator columns at a time: one tcgen05.ld per step; bf16 / f32 / e4m3 rows are staged
         // in rows of kRowBytes (64 / 128 / 128 bytes, swizzled like the store's tensor map) and
@@ -513,7 +667,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 __syncwarp();
                 if (lane == 0) {
                     if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
-                    else mbar_arrive_remote(bar_tmem_empty + e, 0);
+                    else mbar_arrive_remote(bar_tmem_empty + e, leader_rank);
                 }
                 continue;
             }
@@ -524,7 +678,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 __syncwarp();
                 if (lane == 0) {
                     if constexpr (kCtas == 1) mbar_arrive(bar_tmem_empty + e);
-                    else mbar_arrive_remote(bar_tmem_empty + e, 0);
+                    else mbar_arrive_remote(bar_tmem_empty + e, leader_rank);
                 }
             };
             if constexpr (kOut == kOutSwiGluFp8) {
@@ -699,6 +853,63 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         }
         if (lane == 0) tma_store_wait<0>();
         __syncwarp();
+      }
+    }
+
+    if constexpr (kSwap) {
+        if (p.cluster_splits > 1) {
+            // Every CTA (pair) of the cluster now holds, in TMEM, the partial sums of one K range of the same tile.  Output rows
+            // (accumulator columns) are dealt out in slices, one per K range: every CTA sends each slice to the CTA that owns it
+            // (same rank within the pair), the owner adds the slices in range order and stores its rows.  The exchange buffer
+            // lies over the stage buffers, which nobody touches once all main loops of the cluster are over.
+            Scheduler sched(p, kCtas, true, cluster_rank);
+            Tile t;
+            const bool has_tile = sched.next(t);
+            const uint32_t num_ranges = p.cluster_splits;
+            const uint32_t n_tile = has_tile ? sched.umma_n(t, kCtas) : 0u;
+            const uint32_t rows_per = (n_tile + num_ranges - 1) / num_ranges;
+            float* red = reinterpret_cast<float*>(smem);       // [source range][row of the slice][128 lanes]
+            tc_fence_before();
+            cluster_sync();
+            tc_fence_after();
+            if (warp >= 4 && has_tile && *abort_flag == 0) {
+                const uint32_t ew = warp - 4;
+                const uint32_t taddr = tmem_base + ((ew * 32) << 16);
+                const uint32_t my_slot = smem_u32(red) + (sched.split * rows_per * kBlockM + ew * 32 + lane) * 4;
+                for (uint32_t s = 0; s * 32 < n_tile; ++s) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(taddr + s * 32, v);
+                    tmem_ld_wait_x32(v);
+                    #pragma unroll
+                    for (uint32_t c = 0; c < 32; ++c) {
+                        const uint32_t row = s * 32 + c;
+                        if (row < n_tile) {
+                            const uint32_t owner = row / rows_per, local = row - owner * rows_per;
+                            st_shared_cluster_u32(mapa_u32(my_slot + local * kBlockM * 4, owner * kCtas + cta_rank), v[c]);
+                        }
+                    }
+                }
+            }
+            cluster_sync();      // release / acquire across the cluster: every slice has arrived
+            if (has_tile && *abort_flag == 0) {
+                const uint32_t rows_left = t.n_end > t.n0 ? t.n_end - t.n0 : 0u;
+                const uint32_t valid = rows_left < n_tile ? rows_left : n_tile;
+                const uint32_t row_lo = sched.split * rows_per;
+                const uint32_t rows_here = row_lo < valid ? (valid - row_lo < rows_per ? valid - row_lo : rows_per) : 0u;
+                constexpr uint32_t kElem = kOut == kOutBf16 ? 2 : 4;
+                for (uint32_t i = threadIdx.x; i < rows_here * kBlockM; i += kNumThreads) {
+                    const uint32_t local = i / kBlockM, col = i % kBlockM;
+                    float acc = red[local * kBlockM + col];
+                    for (uint32_t src = 1; src < num_ranges; ++src) acc += red[(src * rows_per + local) * kBlockM + col];
+                    const uint32_t col_out = t.m0 + cta_rank * kBlockM + col;
+                    if (col_out < t.m_end) {
+                        uint8_t* dst = static_cast<uint8_t*>(p.out_ptr) +
+                                       ((static_cast<size_t>(t.gd) * p.out_group_rows + t.n0 + row_lo + local) * p.out_ld + col_out) * kElem;
+                        if constexpr (kOut == kOutBf16 || kOut == kOutF32) store_output<kOut>(dst, acc, p);
+                    }
+                }
+            }
+        }
     }
 
     tc_fence_before();
@@ -711,10 +922,14 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 
 // Bytes of dynamic shared memory the kernel needs for a configuration (host side).
 inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t ctas, uint32_t out_kind, uint32_t stages, uint32_t sfa_words, uint32_t sfb_words,
-                                uint32_t halves) {
+                                uint32_t halves, bool swap = false) {
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
     const uint32_t per_stage = halves * (kBlockM * kBlockKBytes + block_n / ctas * kBlockKBytes) + 512 * sfa_words + sf_block_n * 4 * sfb_words;
-    return 1024 + stages * per_stage + 8 * epilogue_buf_bytes(out_kind) + (4 * kMaxStages + 4) * 8 + 16;
+    return 1024 + stages * per_stage + (swap ? 0u : 8 * epilogue_buf_bytes(out_kind)) + (4 * kMaxStages + 4) * 8 + 16;
+}
+// Bytes of the operand stage buffers alone: the K-range exchange of the swapped family lays its buffer over them.
+inline uint32_t gemm_stage_bytes(uint32_t block_n, uint32_t ctas, uint32_t stages, uint32_t halves) {
+    return stages * halves * (kBlockM * kBlockKBytes + block_n / ctas * kBlockKBytes);
 }
 
 }  // namespace dg

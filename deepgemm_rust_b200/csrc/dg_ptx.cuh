@@ -355,6 +355,10 @@ DG_DEVICE uint32_t cvt_e2m1x8(const float* v) {
 // Separate rounded multiply and add on purpose: a fused multiply-add would keep the sign of an
 // underflowing product.
 DG_DEVICE float scale_pos_zero(float v, float inv) { return __fadd_rn(__fmul_rn(v, inv), 0.0f); }
+// Store to the shared memory of a CTA of this cluster (address from mapa_u32).
+DG_DEVICE void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 DG_DEVICE void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }

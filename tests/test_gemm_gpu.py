@@ -28,6 +28,16 @@ def ctx():
     c.close()
 
 
+# DG_SWAP pins the tile family: "0" activation rows on the UMMA M dimension (128 / 256-row tiles), "1" weight rows on UMMA M and
+# activation rows on a UMMA N that follows the rows a tile has; None leaves the choice to the heuristic
+both_families = pytest.mark.parametrize("family", ["0", "1"])
+
+
+def pin_family(monkeypatch, family):
+    if family is not None:
+        monkeypatch.setenv("DG_SWAP", family)
+
+
 def lp(q, sf, rows, k, bits=8, gran=128):
     return dg.LpOperand(dev(q), dev(sf), rows, k, k, bits, gran)
 
@@ -72,7 +82,9 @@ def run_dense(ctx, m, n, k, gran=128, out_kind=0, alpha=None, seed=0, b_tile_sca
     (384, 2112, 1024),    # N not a multiple of the tile width
     (1, 64, 256), (129, 72, 384),
 ])
-def test_dense_fp8_small(ctx, m, n, k):
+@both_families
+def test_dense_fp8_small(ctx, m, n, k, family, monkeypatch):
+    pin_family(monkeypatch, family)
     run_dense(ctx, m, n, k)
 
 
@@ -103,14 +115,65 @@ def test_dense_fp8_every_tile_shape(ctx, ctas, block_n, slabs, monkeypatch):
 
 @pytest.mark.parametrize("splits", [2, 3, 5])
 def test_dense_fp8_split_k(ctx, splits, monkeypatch):
-    # K ranges computed by different CTAs, f32 partials summed by a second kernel; ranges are multiples of 4 k-blocks,
-    # the last one may be shorter (K = 36 k-blocks here)
+    # first tile family: K ranges computed by different CTAs, f32 partials summed by a second kernel; ranges are multiples of
+    # 4 k-blocks, the last one may be shorter (K = 36 k-blocks here)
     monkeypatch.setenv("DG_SPLITS", str(splits))
+    monkeypatch.setenv("DG_SWAP", "0")
     cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 1000, 4608))
-    assert cfg.num_splits == splits
+    assert cfg.num_splits == splits and not cfg.swap_ab
     run_dense(ctx, 128, 1000, 4608, seed=splits)
     run_dense(ctx, 100, 512, 4608, out_kind=1, seed=splits, alpha=0.5)
     run_dense(ctx, 300, 256, 9216, out_kind=0, seed=splits, alpha=2.0)
+
+
+@pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("splits", [1, 2, 3, 4, 5, 7, 8])
+def test_swapped_dense_k_ranges_in_a_cluster(ctx, splits, ctas, monkeypatch):
+    # swapped family (what the reference runs for few rows: heuristics_sm100.rs:341-452): weight rows on UMMA M, the rows of A on
+    # UMMA N; K is cut into `splits` ranges, one per CTA (or pair) of a cluster, whose partial tiles are summed through shared
+    # memory in range order.  Ranges may start inside a scale word (37 k-blocks here), N is ragged, M takes the values a
+    # decode batch has.  The sum does not depend on how the launch went: two runs give the same bits.
+    if splits * ctas > 8:
+        pytest.skip("a cluster holds at most 8 CTAs")
+    monkeypatch.setenv("DG_SPLITS", str(splits))
+    monkeypatch.setenv("DG_CTAS", str(ctas))
+    cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 1000, 4736))
+    assert cfg.swap_ab and cfg.num_splits == splits and cfg.cluster_n == ctas
+    for m in (1, 16, 17, 100, 128, 250):
+        run_dense(ctx, m, 1000, 4736, seed=splits + m)
+    run_dense(ctx, 100, 520, 4736, out_kind=1, seed=splits, alpha=0.5)
+    run_dense(ctx, 128, 328, 2176, gran=32, seed=splits)
+    _, aq, asf = fp8_operand_1d(77, 4736, 5)
+    _, bq, bsf = fp8_operand_1d(1000, 4736, 6)
+    outs = []
+    for _ in range(2):
+        d = torch.zeros((77, 1000), dtype=torch.float32, device="cuda")
+        dg.fp8_fp4_gemm_dev(ctx, lp(aq, asf, 77, 4736), lp(bq, bsf, 1000, 4736), dg.Sm100Out.F32(d, 1000))
+        ctx.sync()
+        outs.append(d)
+    assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("ctas", [1, 2])
+@pytest.mark.parametrize("block_n", [16, 32, 48, 96, 112, 128, 160, 208, 256])
+@pytest.mark.parametrize("slabs", [1, 2])
+def test_swapped_dense_every_width(ctx, ctas, block_n, slabs, monkeypatch):
+    # every UMMA N the swapped family can issue (multiples of 16, of 32 for a CTA pair), one and two K slabs per stage,
+    # with a problem that has fewer rows than the tile, exactly as many, and several tiles of rows
+    if block_n % (16 * ctas) != 0:
+        pytest.skip("tile width not issuable")
+    monkeypatch.setenv("DG_SWAP", "1")
+    monkeypatch.setenv("DG_BLOCK_N", str(block_n))
+    monkeypatch.setenv("DG_CTAS", str(ctas))
+    monkeypatch.setenv("DG_K_SLABS", str(slabs))
+    try:
+        cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, block_n, 1000, 1152))
+    except dg.DgError:
+        pytest.skip("this tile does not fit three stages of two slabs")
+    assert cfg.swap_ab and cfg.block_m == block_n and cfg.block_n == 128 * ctas and cfg.block_k == 128 * slabs
+    for m in (max(1, block_n - 9), block_n, 2 * block_n + 5):
+        run_dense(ctx, m, 1000, 1152, seed=block_n + m)
+    run_dense(ctx, block_n, 712, 1152, out_kind=1, seed=block_n)
 
 
 def test_dense_fp8_matches_scalar_reference_and_golden(ctx):
@@ -127,11 +190,15 @@ def test_dense_fp8_matches_scalar_reference_and_golden(ctx):
 
 @pytest.mark.parametrize("gran", [32])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 512), (200, 320, 1152)])
-def test_dense_fp8_gran32(ctx, m, n, k, gran):
+@both_families
+def test_dense_fp8_gran32(ctx, m, n, k, gran, family, monkeypatch):
+    pin_family(monkeypatch, family)
     run_dense(ctx, m, n, k, gran=gran)
 
 
-def test_dense_f32_and_alpha(ctx):
+@both_families
+def test_dense_f32_and_alpha(ctx, family, monkeypatch):
+    pin_family(monkeypatch, family)
     run_dense(ctx, 256, 384, 1024, out_kind=1)
     run_dense(ctx, 256, 384, 1024, out_kind=0, alpha=0.125)
     run_dense(ctx, 128, 96, 512, out_kind=1, alpha=3.0)
@@ -139,7 +206,9 @@ def test_dense_f32_and_alpha(ctx):
 
 @pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("out_kind", [0, 1])
-def test_dense_accumulate_adds_into_the_output(ctx, out_kind, ctas, monkeypatch):
+@both_families
+def test_dense_accumulate_adds_into_the_output(ctx, out_kind, ctas, family, monkeypatch):
+    pin_family(monkeypatch, family)
     # D += A.B^T (with_accumulation, ops_sm100.rs:150): tiles are added to what the output holds. f32 outputs add
     # in f32; bf16 outputs add the bf16-rounded tile to the bf16 addend and round once more, so the bound is
     # two bf16 roundings. Ragged M and N: rows and columns outside the problem must stay untouched.
@@ -216,7 +285,9 @@ def contiguous_layout(group_sizes, alignment=128):
     ([200, 0, 300, 0, 0, 129], 512, 768),       # empty experts, multi-tile experts
 ])
 @pytest.mark.parametrize("ctas", [1, 2])
-def test_m_grouped_contiguous(ctx, sizes, n, k, ctas, monkeypatch):
+@both_families
+def test_m_grouped_contiguous(ctx, sizes, n, k, ctas, family, monkeypatch):
+    pin_family(monkeypatch, family)
     # with a CTA pair the 256-row tile of a group's tail reaches into the next group's rows: those rows are
     # computed but must never be stored
     monkeypatch.setenv("DG_CTAS", str(ctas))
@@ -255,7 +326,9 @@ def test_m_grouped_contiguous(ctx, sizes, n, k, ctas, monkeypatch):
 @pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("out_kind", [0, 1])
 @pytest.mark.parametrize("alignment", [64, 32, 16, 256])
-def test_m_grouped_contiguous_other_alignments(ctx, alignment, out_kind, ctas, monkeypatch):
+@both_families
+def test_m_grouped_contiguous_other_alignments(ctx, alignment, out_kind, ctas, family, monkeypatch):
+    pin_family(monkeypatch, family)
     # set_mk_alignment_for_contiguous_layout (types.rs:195): groups start at multiples of 16..256 rows.  Tiles stay 128 / 256
     # rows tall, so a group's last tile runs into the following groups' rows: those must come out as their own group computes
     # them, never as this tile computes them (several rounds: a wrong store would race with the right one)
@@ -300,7 +373,9 @@ def test_m_grouped_contiguous_other_alignments(ctx, alignment, out_kind, ctas, m
     ([0, 256, 17, 129, 255, 16, 0, 1], 256, 384, 1024),
     ([100, 7], 100, 128, 256),                               # m_max not a multiple of the tile
 ])
-def test_m_grouped_masked(ctx, masked, m_max, n, k, ctas, monkeypatch):
+@both_families
+def test_m_grouped_masked(ctx, masked, m_max, n, k, ctas, family, monkeypatch):
+    pin_family(monkeypatch, family)
     monkeypatch.setenv("DG_CTAS", str(ctas))
     groups = len(masked)
     masked_m = np.array(masked, np.int32)
@@ -325,7 +400,8 @@ def test_m_grouped_masked(ctx, masked, m_max, n, k, ctas, monkeypatch):
     assert diff <= TIGHT_BF16, diff
     # rows of a group whose tiles were never scheduled keep the caller's contents (no stray writes)
     for g in range(groups):
-        first_untouched = g * m_max + ((masked[g] + 128 * ctas - 1) // (128 * ctas)) * 128 * ctas
+        # first family: whole 128- or 256-row tiles; swapped family: exactly the valid rows
+        first_untouched = g * m_max + (masked[g] if family == "1" else ((masked[g] + 128 * ctas - 1) // (128 * ctas)) * 128 * ctas)
         if first_untouched < (g + 1) * m_max:
             assert np.isnan(dn[first_untouched:(g + 1) * m_max]).all()
 
@@ -401,7 +477,9 @@ def test_masked_fp8_requant_feeds_next_gemm(ctx):
 
 
 @pytest.mark.parametrize("m,n,k,rule", [(128, 256, 512, 0), (256, 512, 768, 1), (8, 8, 128, 0), (200, 192, 1280, 1)])
-def test_dense_mxfp4(ctx, m, n, k, rule):
+@both_families
+def test_dense_mxfp4(ctx, m, n, k, rule, family, monkeypatch):
+    pin_family(monkeypatch, family)
     # reference e2e MXFP4 shapes (tests/e2e.rs:266-350) against mxfp4_gemm_reference (reference.rs:293-329)
     _, aq, asf = fp4_operand(m, k, 51, 1, rule)
     _, bq, bsf = fp4_operand(n, k, 52, 1, rule)
@@ -415,7 +493,9 @@ def test_dense_mxfp4(ctx, m, n, k, rule):
 
 @pytest.mark.parametrize("a_bits,b_bits,gran8", [(8, 4, 128), (8, 4, 32), (4, 8, 128)])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 448, 1408)])
-def test_dense_mixed_fp8_fp4(ctx, m, n, k, a_bits, b_bits, gran8):
+@both_families
+def test_dense_mixed_fp8_fp4(ctx, m, n, k, a_bits, b_bits, gran8, family, monkeypatch):
+    pin_family(monkeypatch, family)
     # e4m3 (per-128 or per-32 scales) against packed e2m1 (per-32 scales) on the byte-operand tensor-core kind
     def operand(rows, bits, seed):
         if bits == 8:
@@ -516,7 +596,9 @@ def test_fp4_convenience_entry_points(ctx):
     assert O.calc_diff(to_f32(out), want) <= TIGHT_BF16
 
 
-def test_m_grouped_mxfp4(ctx):
+@both_families
+def test_m_grouped_mxfp4(ctx, family, monkeypatch):
+    pin_family(monkeypatch, family)
     groups, gm, n, k = 4, 128, 256, 512     # tests/e2e.rs:439-500
     _, aq, asf = fp4_operand(groups * gm, k, 61, 1, 1)
     _, bq, bsf = fp4_operand(groups * n, k, 62, groups, 1)
