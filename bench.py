@@ -1009,7 +1009,8 @@ def main():
     extra_launches = 0
     if dense is not None:
         d_ms = timed(dense.step, args.steps) if moe is not None else ms_per_step
-        parts["dense_fp8"] = {"tflops": dense.flops * world / (d_ms * 1e-3) / 1e12, "ms_per_step": d_ms, "parallelism": "replica per GPU"}
+        parts["dense_fp8"] = {"tflops": dense.flops * world / (d_ms * 1e-3) / 1e12, "ms_per_step": d_ms, "parallelism": "replica per GPU",
+                              "launch_us_in_step_rank0": {k[6:]: round(v, 1) for k, v in launch_us.items() if k.startswith("dense ")}}
     if moe is not None:
         m_ms = timed(moe.step, args.steps) if dense is not None else ms_per_step
         gemm_ms, gemm_rows = moe.gate_up_alone()

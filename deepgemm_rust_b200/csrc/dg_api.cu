@@ -292,15 +292,15 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out,
         }
     }
     }
-    // ---- the swapped family: weight rows on UMMA M, activation rows on UMMA N (bf16 / f32 outputs).  Chosen for dense GEMMs
-    // with at most 256 activation rows, where the first family would leave most of its 128-row tiles empty and, having few
-    // tiles, fill few SMs; DG_SWAP=1 forces it wherever it applies, DG_SWAP=0 forbids it.
+    // ---- the swapped family: weight rows on UMMA M, activation rows on UMMA N (bf16 / f32 outputs).  DG_SWAP=1 selects it
+    // wherever it applies.  It is not the default anywhere yet: measured on B200 it streams the weights of skinny and
+    // small-group problems more slowly than the first family, which keeps more weight bytes in flight per SM.
     {
         const char* force_swap = getenv("DG_SWAP");
         const bool forced = force_swap && atoi(force_swap) != 0, forbidden = force_swap && atoi(force_swap) == 0;
         const bool plain_out = d->cd_dtype == DG_OUT_BF16 || d->cd_dtype == DG_OUT_F32;
         const bool dense = d->gemm_type == DG_GEMM_NORMAL || d->gemm_type == DG_GEMM_BATCHED;
-        const bool want = forced || (d->gemm_type == DG_GEMM_NORMAL && d->m <= 256);
+        const bool want = forced;
         if (plain_out && want && !forbidden) {
             uint32_t s_n = 0, s_ctas = 0, s_halves = 0, s_stages = 0, s_accum = 0, s_split = 1, s_tiles = 0;
             double s_cost = 0;

@@ -135,6 +135,7 @@ def test_swapped_dense_k_ranges_in_a_cluster(ctx, splits, ctas, monkeypatch):
     # decode batch has.  The sum does not depend on how the launch went: two runs give the same bits.
     if splits * ctas > 8:
         pytest.skip("a cluster holds at most 8 CTAs")
+    monkeypatch.setenv("DG_SWAP", "1")
     monkeypatch.setenv("DG_SPLITS", str(splits))
     monkeypatch.setenv("DG_CTAS", str(ctas))
     cfg = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 1000, 4736))
