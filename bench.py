@@ -404,13 +404,17 @@ class MoeWork:
         m_idx[::align] = torch.arange(groups, dtype=torch.int32, device=dev)
         w1q, w1sf = self.expert_weights(experts, 1)
         w2q, w2sf = self.expert_weights(experts, 2)
-        h = torch.empty((rows, c["gate_up_n"]), dtype=torch.bfloat16, device=dev)
-        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(xq, xsf, rows, c["hidden"], c["hidden"]), m_idx,
-                                                 dg.LpOperand(w1q, w1sf, groups * c["gate_up_n"], c["hidden"], c["hidden"]),
-                                                 dg.Sm100Out.Bf16(h, c["gate_up_n"]), groups)
-        actq, actsf = dg.silu_mul_cast_fp8_sf_dev(ctx, h, c["gate_up_n"], rows, c["down_k"], 128)
+        a_op, w1 = dg.LpOperand(xq, xsf, rows, c["hidden"], c["hidden"]), dg.LpOperand(w1q, w1sf, groups * c["gate_up_n"], c["hidden"], c["hidden"])
+        if self.fused_act:
+            actq = torch.empty((rows, c["down_k"]), dtype=torch.uint8, device=dev)
+            actsf = dg.alloc_sf(ctx, rows, c["down_k"], 32)
+            dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a_op, m_idx, w1, dg.Sm100Out.SwiGluFp8(actq, c["down_k"], actsf), groups)
+        else:
+            h = torch.empty((rows, c["gate_up_n"]), dtype=torch.bfloat16, device=dev)
+            dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, a_op, m_idx, w1, dg.Sm100Out.Bf16(h, c["gate_up_n"]), groups)
+            actq, actsf = dg.silu_mul_cast_fp8_sf_dev(ctx, h, c["gate_up_n"], rows, c["down_k"], 128)
         y = torch.empty((rows, c["down_n"]), dtype=torch.bfloat16, device=dev)
-        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(actq, actsf, rows, c["down_k"], c["down_k"]), m_idx,
+        dg.m_grouped_fp8_fp4_gemm_contiguous_dev(ctx, dg.LpOperand(actq, actsf, rows, c["down_k"], c["down_k"], 8, self.act_gran), m_idx,
                                                  dg.LpOperand(w2q, w2sf, groups * c["down_n"], c["down_k"], c["down_k"]),
                                                  dg.Sm100Out.Bf16(y, c["down_n"]), groups)
         pos = (torch.arange(groups, dtype=torch.int32, device=dev) * align).view(sample_tokens, c["topk"]).contiguous()
@@ -1027,7 +1031,7 @@ def main():
     if not args.no_extras:
         parity = {}
         ok = 1
-        if moe is not None and moe.peer is not None and not moe.fused_act and moe.pipe is None:
+        if moe is not None and moe.peer is not None and moe.pipe is None:
             good, n_tok = moe.parity_check(moe.step())
             ok = int(good)
             parity["moe_tokens_checked"] = int(sum_over_ranks(n_tok))

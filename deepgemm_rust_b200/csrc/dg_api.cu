@@ -721,6 +721,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.out_ptr = out->buf;
     p.out_ld = out->ld;
     p.accumulate = e.accumulate ? 1 : 0;
+    p.tc_util = (e.tc_util == 0 || e.tc_util > 100) ? 100 : e.tc_util;      // 0 means "unset", as in ops_sm100.rs:518-522
     p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges summed by the second kernel alpha is applied there
     p.alpha = e.alpha;
     p.sfd = out->sfd;

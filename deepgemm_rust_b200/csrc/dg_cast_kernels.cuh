@@ -259,9 +259,19 @@ __global__ void __launch_bounds__(256) dg_splitk_reduce_kernel(const float* __re
     if (i >= static_cast<uint64_t>(m) * chunks) return;
     const uint32_t row = static_cast<uint32_t>(i / chunks), c = static_cast<uint32_t>(i % chunks) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t s = 0; s < splits; ++s) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * m + row) * pitch + c));
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    const float* first = partial + static_cast<size_t>(row) * pitch + c;
+    const size_t plane = static_cast<size_t>(m) * pitch;
+    // four planes' loads in flight before the first add (the planes mostly sit in L2: latency, not bandwidth, is the cost);
+    // the adds keep the order s = 0, 1, ...
+    for (uint32_t s = 0; s < splits; s += 4) {
+        float4 v[4];
+        #pragma unroll
+        for (uint32_t u = 0; u < 4; ++u)
+            v[u] = s + u < splits ? __ldg(reinterpret_cast<const float4*>(first + (s + u) * plane)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        #pragma unroll
+        for (uint32_t u = 0; u < 4; ++u) {
+            if (s + u < splits) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+        }
     }
     acc.x *= alpha; acc.y *= alpha; acc.z *= alpha; acc.w *= alpha;
     const float vals[4] = {acc.x, acc.y, acc.z, acc.w};

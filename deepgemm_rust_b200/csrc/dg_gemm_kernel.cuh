@@ -79,6 +79,8 @@ struct GemmParams {
     void* out_ptr;             // output base and leading dimension (elements), used by those row-by-row stores only
     uint32_t out_ld;
     uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
+    uint32_t tc_util;          // tensor-core duty cycle in percent (100: no pause); below 100 the UMMA warp idles after every k-block
+                               // for (100 - tc_util) / tc_util times the k-block's tensor time (bf16_gemm_sm100.rs:358-371)
     float alpha;
     uint32_t sfd_stride;       // output scale words: stride between word columns (fp8 output)
     uint32_t cluster_splits;   // kSwap, dense: K ranges handled by the CTAs (pairs) of one cluster and summed through shared memory
@@ -333,7 +335,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     uint64_t* bar_sf_ready = bars + 3 * kMaxStages;  // scale words re-ordered (pair: both CTAs, on rank 0)
     uint64_t* bar_tmem_full = bars + 4 * kMaxStages;
     uint64_t* bar_tmem_empty = bars + 4 * kMaxStages + 2;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kMaxStages + 4);
+    uint64_t* bar_tc = bars + 4 * kMaxStages + 4;     // the UMMAs of a k-block finished (only with a tensor-core duty cycle below 100 %)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * kMaxStages + 5);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     if (threadIdx.x == 0) {
@@ -347,6 +350,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             mbar_init(bar_tmem_full + e, 1);
             mbar_init(bar_tmem_empty + e, 4 * kCtas);
         }
+        mbar_init(bar_tc, 1);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&tmap_a);
@@ -441,7 +445,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         if (cta_rank == 0) {
             Scheduler sched(p, kCtas, kSwap, cluster_rank);
             Tile t;
-            uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0;
+            uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0, tc_phase = 0;
             const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
 #ifdef DG_PROFILE
@@ -528,6 +532,21 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         }
                     }
                     __syncwarp();
+                    if (p.tc_util < 100) {
+                        // let the tensor cores rest: wait until this k-block's UMMAs are done, then idle for the requested share
+                        if (leader_lane) {
+                            if constexpr (kCtas == 1) umma_commit(bar_tc);
+                            else umma_commit_2cta(bar_tc, static_cast<uint16_t>(1u << leader_rank));
+                        }
+                        __syncwarp();
+                        if (!mbar_wait_warp(bar_tc, tc_phase, abort_flag, p.status, 0x480)) { ok = false; break; }
+                        tc_phase ^= 1;
+                        const long long busy = 4ll * n_tile * halves;      // 2 * 128 * N * (128 * halves) / 8192 cycles per k-block and SM
+                        const long long idle = (100ll - p.tc_util) * busy / p.tc_util;
+                        const long long t0 = clock64();
+                        while (clock64() - t0 < idle) {}
+                        __syncwarp();
+                    }
                     DG_PROF_ADD(3, t_issue);
                     if (++stage == num_stages) { stage = 0; phase ^= 1; }
                 }
@@ -925,7 +944,7 @@ inline uint32_t gemm_smem_bytes(uint32_t block_n, uint32_t ctas, uint32_t out_ki
                                 uint32_t halves, bool swap = false) {
     const uint32_t sf_block_n = (block_n + 127) / 128 * 128;
     const uint32_t per_stage = halves * (kBlockM * kBlockKBytes + block_n / ctas * kBlockKBytes) + 512 * sfa_words + sf_block_n * 4 * sfb_words;
-    return 1024 + stages * per_stage + (swap ? 0u : 8 * epilogue_buf_bytes(out_kind)) + (4 * kMaxStages + 4) * 8 + 16;
+    return 1024 + stages * per_stage + (swap ? 0u : 8 * epilogue_buf_bytes(out_kind)) + (4 * kMaxStages + 5) * 8 + 16;
 }
 // Bytes of the operand stage buffers alone: the K-range exchange of the swapped family lays its buffer over them.
 inline uint32_t gemm_stage_bytes(uint32_t block_n, uint32_t ctas, uint32_t stages, uint32_t halves) {

@@ -82,7 +82,8 @@ typedef struct {
     float alpha;
     int has_alpha;
     int accumulate;       /* D += A.B^T (dense, masked and batched calls; bf16 or f32 outputs; not with alpha) */
-    uint32_t tc_util;     /* accepted, ignored (100 = unthrottled) */
+    uint32_t tc_util;     /* tensor-core duty cycle in percent (cuda/bf16_gemm_sm100.rs:358-371): below 100 the UMMA warp pauses after
+                             every k-block for (100 - tc_util) / tc_util of that k-block's tensor time; 0 or 100 = no pause */
 } dg_epilogue;
 
 /* ops_sm100.rs:719 (fp8_fp4_gemm_dev): D[m,n] = alpha * A[m,k] . B[n,k]^T */

@@ -206,6 +206,30 @@ def test_dense_f32_and_alpha(ctx, family, monkeypatch):
 
 
 @pytest.mark.parametrize("ctas", [1, 2])
+def test_tensor_core_duty_cycle_pauses_without_changing_results(ctx, ctas, monkeypatch):
+    # Sm100Epilogue::tc_util (ops_sm100.rs:114-131; device side cuda/bf16_gemm_sm100.rs:358-371): below 100 the UMMA warp idles after
+    # every k-block.  The product is bit-identical, and a 20 % duty cycle takes visibly longer than an unthrottled run.
+    monkeypatch.setenv("DG_CTAS", str(ctas))
+    m, n, k = 2048, 2048, 8192
+    _, aq, asf = fp8_operand_1d(m, k, 91)
+    _, bq, bsf = fp8_operand_1d(n, k, 92)
+    a, b = lp(aq, asf, m, k), lp(bq, bsf, n, k)
+    outs, times = [], []
+    for util in (100, 20, 0):
+        d = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        for _ in range(2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dg.fp8_fp4_gemm_dev(ctx, a, b, dg.Sm100Out.Bf16(d, n), dg.Sm100Epilogue(tc_util=util))
+            e1.record()
+            ctx.sync()
+        outs.append(d)
+        times.append(e0.elapsed_time(e1))
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert times[1] > 1.3 * times[0] and times[2] < 1.3 * times[0]     # 0 means "unset" = unthrottled
+
+
+@pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("out_kind", [0, 1])
 @both_families
 def test_dense_accumulate_adds_into_the_output(ctx, out_kind, ctas, family, monkeypatch):
