@@ -15,6 +15,7 @@
 #include "../../include/dgb200.h"
 #include "dg_cast_kernels.cuh"
 #include "dg_gemm_kernel.cuh"
+#include "dg_gemm_f32scale.cuh"
 #include "dg_moe_kernels.cuh"
 
 namespace {
@@ -853,8 +854,93 @@ int dg_fp8_fp4_bmm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, 
 
 // ------------------------------------------------------------ f32-scale entry points
 // The reference's older API hands scales over as f32 (activations transposed by transform_sf, weights one per
-// 128x128 tile).  Like the reference on Blackwell (ops_sm100.rs:1414-1605) these entry points pack the exponents into
-// UE8M0 words (mantissas are dropped: the scales must be powers of two to be exact) and run the block-scaled kernel.
+// 128x128 tile).  By default they are applied exactly, K block by K block, as the reference's CPU definition does
+// (reference.rs:85-208): dg_gemm_f32scale_kernel.  With DG_F32_SCALES=exponent the calls do what the reference itself does on
+// Blackwell (ops_sm100.rs:1414-1605): pack the exponents into UE8M0 words (mantissas are dropped, so the scales must be powers
+// of two to be exact) and run the block-scaled kernel, which is about three times faster.
+static int launch_f32scale(dg_ctx* ctx, uint32_t type, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
+                           const float* sfb, uint32_t m, uint32_t n, uint32_t k, uint32_t groups, const uint32_t* layout, uint16_t* out,
+                           uint32_t out_ld) {
+    if (m == 0 || n == 0) return DG_OK;
+    const bool contiguous = type == DG_GEMM_M_GROUPED_CONTIGUOUS;
+    const uint32_t a_groups = (type == DG_GEMM_NORMAL || contiguous) ? 1 : groups;
+    const uint32_t b_groups = type == DG_GEMM_NORMAL ? 1 : groups;
+    const uint32_t align = g_mk_alignment.load();
+    if (contiguous && align % 32 != 0) return fail(DG_ERR_UNSUPPORTED, "the exact f32-scale path needs an mk alignment of at least 32");
+    if (a_ld < k || b_ld < k || a_ld % 16 != 0 || b_ld % 16 != 0) return fail(DG_ERR_SHAPE, "leading dimensions must be >= k and multiples of 16 bytes");
+    if (out_ld < n || (static_cast<size_t>(out_ld) * 2) % 16 != 0) return fail(DG_ERR_SHAPE, "output ld (%u) must be >= n and a multiple of 8 elements", out_ld);
+    CUtensorMap maps[3];
+    int rc;
+    {
+        uint64_t dims[3] = {k, m, a_groups};
+        uint64_t strides[2] = {a_ld, static_cast<uint64_t>(a_ld) * m};
+        uint32_t box[3] = {128, dg::kBlockM, 1};
+        rc = encode_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
+        if (rc) return rc;
+        uint64_t bdims[3] = {k, n, b_groups};
+        uint64_t bstrides[2] = {b_ld, static_cast<uint64_t>(b_ld) * n};
+        uint32_t bbox[3] = {128, dg::kF32BlockN, 1};
+        rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, b, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
+        if (rc) return rc;
+        const uint64_t pitch = static_cast<uint64_t>(out_ld) * 2;
+        uint64_t ddims[3] = {n, m, a_groups};
+        uint64_t dstrides[2] = {pitch, pitch * m};
+        uint32_t dbox[3] = {32, 32, 1};
+        rc = encode_map(&maps[2], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, ddims, dstrides, dbox, CU_TENSOR_MAP_SWIZZLE_64B, "D");
+        if (rc) return rc;
+    }
+    dg::F32ScaleParams q;
+    memset(&q, 0, sizeof(q));
+    dg::GemmParams& p = q.g;
+    p.m = m; p.n = n; p.k = k;
+    p.num_groups = groups;
+    p.gemm_type = type;
+    p.block_n = p.tile_n = dg::kF32BlockN;
+    p.block_k_elems = 128;
+    p.num_splits = 1;
+    p.cluster_splits = 1;
+    p.num_accum_stages = 2;
+    p.mk_alignment = align;
+    p.grouped_layout = layout;
+    p.status = ctx->status;
+    uint32_t stages = dg::kMaxStages;
+    while (stages > 1 && dg::f32scale_smem_bytes(stages) > kSmemCapacity) --stages;
+    p.num_stages = stages;
+    q.sfa_t = a_sf_t;
+    q.sfb = sfb;
+    q.sfa_stride = align4(m);
+    q.k_blocks = k / 128;
+    q.n_blocks128 = ceil_div(n, 128);
+    const uint32_t smem = dg::f32scale_smem_bytes(stages);
+    DG_CUDA(cudaSetDevice(ctx->ordinal));
+    {
+        static std::atomic<uint64_t> configured{0};
+        if (ctx->ordinal >= 64 || !(configured.load() & (1ull << ctx->ordinal))) {
+            DG_CUDA(cudaFuncSetAttribute(dg::dg_gemm_f32scale_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemCapacity)));
+            if (ctx->ordinal < 64) configured.fetch_or(1ull << ctx->ordinal);
+        }
+    }
+    uint32_t grid = static_cast<uint32_t>(ctx->num_sms);
+    if (type == DG_GEMM_NORMAL || type == DG_GEMM_BATCHED) {
+        const uint64_t tiles = static_cast<uint64_t>(ceil_div(m, dg::kBlockM)) * ceil_div(n, dg::kF32BlockN) * (type == DG_GEMM_BATCHED ? groups : 1);
+        if (tiles < grid) grid = static_cast<uint32_t>(tiles);
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(dg::kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    const cudaError_t ce = cudaLaunchKernelEx(&cfg, dg::dg_gemm_f32scale_kernel, q, maps[0], maps[1], maps[2]);
+    if (ce != cudaSuccess) return fail(DG_ERR_DRIVER, "kernel launch failed: %s", cudaGetErrorString(ce));
+    return DG_OK;
+}
+
 static int bridge_common(dg_ctx* ctx, uint32_t type, const uint8_t* a, uint32_t a_ld, const float* a_sf_t, const uint8_t* b, uint32_t b_ld,
                          const float* sfb, uint32_t m, uint32_t n, uint32_t k, uint32_t groups, const uint32_t* layout, uint32_t expected_m,
                          uint16_t* out, uint32_t out_ld) {
@@ -865,6 +951,22 @@ static int bridge_common(dg_ctx* ctx, uint32_t type, const uint8_t* a, uint32_t 
     const bool contiguous = type == DG_GEMM_M_GROUPED_CONTIGUOUS;
     const uint32_t a_groups = (type == DG_GEMM_NORMAL || contiguous) ? 1 : groups;
     const uint32_t b_groups = type == DG_GEMM_NORMAL ? 1 : groups;
+    {
+        const char* mode = getenv("DG_F32_SCALES");
+        if (!(mode && strcmp(mode, "exponent") == 0)) {
+            const uint32_t* table = layout;
+            if (contiguous) {
+                // the group-end table the scheduler walks, built from m_indices in the context's scratch
+                int rc = ensure_group_ends(ctx, groups);
+                if (rc) return rc;
+                DG_CUDA(cudaSetDevice(ctx->ordinal));
+                rc = run_group_ends(ctx, reinterpret_cast<const int32_t*>(layout), m, groups, ctx->group_ends);
+                if (rc) return rc;
+                table = ctx->group_ends;
+            }
+            return launch_f32scale(ctx, type, a, a_ld, a_sf_t, b, b_ld, sfb, m, n, k, groups, table, out, out_ld);
+        }
+    }
     const size_t need[2] = {dg_sf_words(m * a_groups, k, 128, a_groups), dg_sf_words(n * b_groups, k, 128, b_groups)};
     DG_CUDA(cudaSetDevice(ctx->ordinal));
     for (int i = 0; i < 2; ++i) {

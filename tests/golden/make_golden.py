@@ -6,6 +6,8 @@ pinned to the reference's known-answer tests.
 fp8_gemm_128x256x512.npz -- the CPU-runnable benchmark case: bf16 N(0,1) inputs (seeds 1001 / 2001)
 quantised to e4m3 with UE8M0 scales (A per 1x128, B per 128x128 tile), and the f32 output of the
 scalar restatement of ref_fp8_gemm_nt (reference.rs:85-114) on those bytes.
+fp8_gemm_f32scale_128x256x512.npz -- the same case as the benchmark contract words it: e4m3 with f32 scales amax / 448, A per
+1x128, B per 128x128 tile (scales with mantissas), and the f32 output of ref_fp8_gemm_nt on those bytes and scales.
 mxfp4_8x8x128.npz -- the modular-pattern case of tests/unit.rs:90-158 through the reference-CPU
 MXFP4 rule and mxfp4_gemm_reference (reference.rs:293-329).
 """
@@ -31,6 +33,11 @@ def main():
     np.savez_compressed(os.path.join(HERE, "fp8_gemm_128x256x512.npz"), a=aq, b=bq, sfa=sfa, sfb=sfb,
                         a_sf_packed=O.transform_sf1d_packed(sfa, k, 128), b_sf_packed=O.transform_sf2d_packed(sfb, n, k),
                         out=out)
+    m, n, k = 128, 256, 512
+    aq, sfa = O.quantize_fp8_f32scale(O.bf16_to_f32_array(a_bits), 1)
+    bq, sfb = O.quantize_fp8_f32scale(O.bf16_to_f32_array(b_bits), 128)
+    np.savez_compressed(os.path.join(HERE, "fp8_gemm_f32scale_128x256x512.npz"), a=aq, b=bq, sfa=sfa, sfb=sfb,
+                        out=O.ref_fp8_gemm_nt(aq, sfa, bq, sfb))
     m, n, k = 8, 8, 128
     a = np.array([[(((i * 13 + j * 7) % 17) - 8.0) / 8.0 for j in range(k)] for i in range(m)], np.float32)
     b = np.array([[(((i * 11 + j * 5) % 19) - 9.0) / 9.0 for j in range(k)] for i in range(n)], np.float32)
