@@ -87,13 +87,17 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
         float amax = 0.0f;
         #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+        // maximum over the lanes that share a scale (16 for per-128, 4 for per-32 scales); a shuffle ladder: warp reductions over
+        // part of a warp run one lane group at a time and measured slower
         #pragma unroll
         for (uint32_t d = kGran / 16; d >= 1; d /= 2) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, d));
         uint32_t e;
         float inv;
         if constexpr (kFp4) {
             e = sf_exp_e2m1(amax, p.rule);
-            inv = p.rule == 0 ? 1.0f / __uint_as_float(e << 23) : __uint_as_float((254u - e) << 23);
+            // rule 0 divides by 2^(e - 127) like the CPU rule: 2^(127 - e) is a normal number down to e = 253, the subnormal
+            // 2^-127 for e = 254, and 1 / inf = 0 for e = 255 (a block maximum beyond 1.5 * 2^127)
+            inv = __uint_as_float(e <= 253u ? (254u - e) << 23 : (e == 254u ? 0x00400000u : 0u));
         } else {
             e = sf_exp_e4m3(amax);
             inv = __uint_as_float((254u - e) << 23);
@@ -113,39 +117,28 @@ __global__ void __launch_bounds__(256) dg_cast_kernel(const CastParams p) {
             }
         }
     }
-    // assemble scale words: exps[h] on lane l belongs to K block (seg*1024 + h*256 + l*8) / kGran
+    // assemble scale words: exps[h] on lane l belongs to K block (seg*1024 + h*256 + l*8) / kGran.  The first lane of every
+    // scale block puts its exponent at the block's byte position and an OR over the lanes of a word collects the four bytes.
     if constexpr (kGran == 128) {
-        // word w of this segment covers loads 2w and 2w+1 (two 128-element blocks each)
+        // word w of this segment covers loads 2w and 2w+1, two 128-element blocks (half-warps) each
         #pragma unroll
         for (uint32_t w = 0; w < kLoads / 2; ++w) {
-            const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, exps[2 * w], 0), e1 = __shfl_sync(0xFFFFFFFFu, exps[2 * w], 16);
-            const uint32_t e2 = __shfl_sync(0xFFFFFFFFu, exps[2 * w + 1], 0), e3 = __shfl_sync(0xFFFFFFFFu, exps[2 * w + 1], 16);
-            const uint32_t col = seg * (kLoads / 2) + w;
-            if (lane == w) {
-                const uint32_t blocks = (p.k + 127) / 128, b0 = col * 4;
-                uint32_t word = e0;
-                if (b0 + 1 < blocks) word |= e1 << 8;
-                if (b0 + 2 < blocks) word |= e2 << 16;
-                if (b0 + 3 < blocks) word |= e3 << 24;
-                words[w][warp] = word;
+            uint32_t mine = 0;
+            if (lane % 16 == 0) {
+                if (k0[2 * w] < p.k) mine |= exps[2 * w] << (8 * (lane / 16));
+                if (k0[2 * w + 1] < p.k) mine |= exps[2 * w + 1] << (16 + 8 * (lane / 16));
             }
+            const uint32_t word = __reduce_or_sync(0xFFFFFFFFu, mine);
+            if (lane == w) words[w][warp] = word;
         }
     } else {
-        // word c of this segment (c = 0..7) covers elements [c*128, +128): lanes 16*(c%2).. of load c/2
+        // load h holds eight 32-element blocks, four lanes each: words 2h (lanes 0..15) and 2h+1 (lanes 16..31)
         #pragma unroll
-        for (uint32_t c = 0; c < 2 * kLoads; ++c) {
-            const uint32_t src_exp = exps[c / 2], base = (c % 2) * 16;
-            const uint32_t b0 = __shfl_sync(0xFFFFFFFFu, src_exp, base), b1 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 4);
-            const uint32_t b2 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 8), b3 = __shfl_sync(0xFFFFFFFFu, src_exp, base + 12);
-            const uint32_t col = seg * 2 * kLoads + c;
-            if (lane == c) {
-                const uint32_t blocks = (p.k + 31) / 32, first = col * 4;
-                uint32_t word = b0;
-                if (first + 1 < blocks) word |= b1 << 8;
-                if (first + 2 < blocks) word |= b2 << 16;
-                if (first + 3 < blocks) word |= b3 << 24;
-                words[c][warp] = word;
-            }
+        for (uint32_t h = 0; h < kLoads; ++h) {
+            uint32_t word = (lane % 4 == 0 && k0[h] < p.k) ? exps[h] << (8 * ((lane / 4) % 4)) : 0u;
+            word |= __shfl_xor_sync(0xFFFFFFFFu, word, 4);
+            word |= __shfl_xor_sync(0xFFFFFFFFu, word, 8);
+            if (lane % 16 == 0) words[2 * h + lane / 16][warp] = word;
         }
     }
     __syncthreads();
