@@ -721,6 +721,16 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     p.mask_rows = (contiguous && align % 32 != 0) ? 1 : 0;
     p.out_ptr = out->buf;
     p.out_ld = out->ld;
+    {
+        // dense problems of a single row block read every weight byte exactly once: those loads carry the L2 evict-first hint
+        // (+9 % on 128 x 7168 x 16384).  Grouped problems with small groups were measured 4 % slower with it (a group's second row
+        // block, running on a neighbouring CTA pair, finds its weight tile gone) and keep plain loads.  DG_STREAM_HINT=0 turns it off.
+        const uint32_t row_block = swap ? plan.umma_n : 128 * plan.ctas;
+        const char* v = getenv("DG_STREAM_HINT");
+        const bool once = pr.type == DG_GEMM_NORMAL && pr.m <= row_block && !(v && strcmp(v, "0") == 0);
+        p.stream_a = (once && swap) ? 1 : 0;
+        p.stream_b = (once && !swap) ? 1 : 0;
+    }
     p.accumulate = e.accumulate ? 1 : 0;
     p.tc_util = (e.tc_util == 0 || e.tc_util > 100) ? 100 : e.tc_util;      // 0 means "unset", as in ops_sm100.rs:518-522
     p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges summed by the second kernel alpha is applied there

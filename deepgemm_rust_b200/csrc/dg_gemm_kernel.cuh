@@ -79,6 +79,8 @@ struct GemmParams {
     void* out_ptr;             // output base and leading dimension (elements), used by those row-by-row stores only
     uint32_t out_ld;
     uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
+    uint32_t stream_a, stream_b;   // that operand is read from DRAM once by the whole launch (weights of a skinny or small-group
+                                   // problem): its loads carry the L2 evict-first hint
     uint32_t tc_util;          // tensor-core duty cycle in percent (100: no pause); below 100 the UMMA warp idles after every k-block
                                // for (100 - tc_util) / tc_util times the k-block's tensor time (bf16_gemm_sm100.rs:358-371)
     float alpha;
@@ -384,6 +386,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         const uint32_t full_bar_leader = kCtas == 2 ? mapa_u32(smem_u32(bar_full), leader_rank) : 0u;
+        const uint64_t stream_policy = (p.stream_a | p.stream_b) ? l2_policy_evict_first() : 0ull;
         while (ok && sched.next(t)) {
             const int32_t row_a = static_cast<int32_t>(t.m0 + cta_rank * kBlockM);
             // fused gate/up activation: rank 0 takes the gate rows [n0, n0 + load_n) of the group's B block, rank 1 the up rows
@@ -427,12 +430,18 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
                         uint8_t* dst_b = smem_b + stage * b_bytes + h * b_half;
                         if constexpr (kCtas == 1) {
-                            tma_load_3d(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
-                            tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
+                            if (p.stream_a) tma_load_3d_hint(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
+                            else tma_load_3d(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
+                            if (p.stream_b) tma_load_3d_hint(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
+                            else tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
                         } else {
                             const uint32_t bar_addr = full_bar_leader + stage * 8;
-                            if (load_a) tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
-                            tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
+                            if (load_a) {
+                                if (p.stream_a) tma_load_3d_2cta_hint(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
+                                else tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
+                            }
+                            if (p.stream_b) tma_load_3d_2cta_hint(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
+                            else tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
                         }
                     }
                 }

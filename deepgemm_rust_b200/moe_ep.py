@@ -363,7 +363,8 @@ class PipelinedPeerMoe:
         return sum(int(e.totals[1].item()) for e in self.exchanges)
 
     def close(self):
-        for e in self.exchanges:
-            e.close()
+        with torch.cuda.stream(self.side):          # the exchanges' context lives on the side stream, and so do their fences
+            for e in self.exchanges:
+                e.close()
         self.exchanges = []
         self.exchange_ctx.close()

@@ -352,3 +352,17 @@ def test_peer_exchange_masked_layout(ctx):
             seen[e] += 1
     finally:
         pe.close()
+
+
+def test_peer_exchange_refuses_a_context_on_another_stream():
+    # the collectives that order the ranks run on torch's current stream; a context whose kernels run elsewhere would race
+    own = dg.DgContext(0, own_stream=True)
+    pe = PeerExpertParallel(own, 8, 2, 16, 512, 256)
+    try:
+        with pytest.raises(RuntimeError):
+            pe._check_stream()
+        with torch.cuda.stream(torch.cuda.ExternalStream(own.stream)):
+            pe._check_stream()
+    finally:
+        pe.close()
+        own.close()
