@@ -260,11 +260,13 @@ def test_dense_accumulate_adds_into_the_output(ctx, out_kind, ctas, family, monk
     assert diff <= (3 * TIGHT_BF16 if out_kind == 0 else TIGHT_F32), diff
 
 
-@pytest.mark.parametrize("m", [128, 4096])
+@pytest.mark.parametrize("m,family", [(128, None), (4096, None), (128, "1"), (77, "1")])
 @pytest.mark.parametrize("n,k", [(2112, 7168), (24576, 1536), (7168, 16384), (4096, 7168), (7168, 2048)])
-def test_dense_fp8_full_size_sampled(ctx, m, n, k):
+def test_dense_fp8_full_size_sampled(ctx, m, n, k, family, monkeypatch):
     # full benchmark shapes: operands quantised on the GPU (bit-exactness of that kernel is its own test),
-    # outputs compared with the oracle on sampled rows / columns including every kind of tile edge
+    # outputs compared with the oracle on sampled rows / columns including every kind of tile edge; the skinny shapes also
+    # through the swapped tile family with its K ranges summed inside a cluster (and with a row count off the 16-row grid)
+    pin_family(monkeypatch, family)
     g = torch.Generator(device="cuda").manual_seed(1000 + n + k)
     a = torch.randn((m, k), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
     b = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32).to(torch.bfloat16)
