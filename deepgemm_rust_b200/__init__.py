@@ -57,7 +57,7 @@ class _Epilogue(C.Structure):
 
 class _Desc(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("gemm_type", "m", "n", "k", "num_groups", "expected_m", "a_bits", "b_bits", "gran_a",
-                                          "gran_b", "cd_dtype", "num_sms")]
+                                          "gran_b", "cd_dtype", "num_sms", "major_a_mn", "major_b_mn")]
 
 
 class _Config(C.Structure):
@@ -623,6 +623,8 @@ class Sm100Desc:
     gran_b: int = 128
     cd_dtype: int = 0
     num_sms: int = 148
+    major_a_mn: bool = False
+    major_b_mn: bool = False
 
 
 @dataclass
@@ -647,7 +649,7 @@ SM100_SMEM_CAPACITY = 232448
 def best_config(desc: Sm100Desc) -> Sm100Config:
     """heuristics_sm100.rs:455"""
     d = _Desc(desc.gemm_type, desc.m, desc.n, desc.k, desc.num_groups, desc.expected_m or desc.m, desc.a_bits, desc.b_bits,
-              desc.gran_a, desc.gran_b, desc.cd_dtype, desc.num_sms)
+              desc.gran_a, desc.gran_b, desc.cd_dtype, desc.num_sms, int(desc.major_a_mn), int(desc.major_b_mn))
     c = _Config()
     _check(_best_config(C.byref(d), C.byref(c)))
     return Sm100Config(bool(c.swap_ab), c.block_m, c.block_n, c.block_k, c.cluster_m, c.cluster_n, c.num_stages,

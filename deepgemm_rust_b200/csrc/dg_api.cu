@@ -196,6 +196,7 @@ int dg_best_config(const dg_desc* d, dg_config* out) {
 static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out, KernelPlan* plan) {
     if (d == nullptr || out == nullptr) return fail(DG_ERR_SHAPE, "null argument");
     if ((d->a_bits != 8 && d->a_bits != 4) || (d->b_bits != 8 && d->b_bits != 4)) return fail(DG_ERR_SHAPE, "operand bits must be 8 or 4");
+    if ((d->major_a_mn && d->a_bits == 4) || (d->major_b_mn && d->b_bits == 4)) return fail(DG_ERR_SHAPE, "FP4 operands must be K-major");
     // two packed e2m1 operands run on kind::mxf4 (256 elements per 128-byte slab); an e4m3 x e2m1 pair runs on
     // kind::mxf8f6f4 with the e2m1 side expanded to one code per byte by the TMA load (128 elements per slab)
     const bool mxf4 = d->a_bits == 4 && d->b_bits == 4;
@@ -245,6 +246,7 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out,
         const uint32_t workers = sms / ctas;
         for (uint32_t bn = step; bn <= 256; bn += step) {
             if (bn % (16 * ctas) != 0) continue;
+            if (d->major_b_mn && (bn / ctas) % 128 != 0) continue;    // an MN-major B tile is made of whole 128-row boxes per CTA
             if (force_n && static_cast<uint32_t>(atoi(force_n)) != bn) continue;
             const uint32_t sf_cols = 4 * sfa_words + ceil_div(bn, 128) * 4 * sfb_words;
             if (bn + sf_cols > 512) continue;
@@ -301,7 +303,7 @@ static int choose_config(const dg_desc* d, uint32_t no_k_ranges, dg_config* out,
         const bool forced = force_swap && atoi(force_swap) != 0, forbidden = force_swap && atoi(force_swap) == 0;
         const bool plain_out = d->cd_dtype == DG_OUT_BF16 || d->cd_dtype == DG_OUT_F32;
         const bool dense = d->gemm_type == DG_GEMM_NORMAL || d->gemm_type == DG_GEMM_BATCHED;
-        const bool want = forced;
+        const bool want = forced && !d->major_a_mn && !d->major_b_mn;   // MN-major operands: first family only
         if (plain_out && want && !forbidden) {
             uint32_t s_n = 0, s_ctas = 0, s_halves = 0, s_stages = 0, s_accum = 0, s_split = 1, s_tiles = 0;
             double s_cost = 0;
@@ -435,10 +437,21 @@ int check_operand(const dg_lp_operand* op, const char* name, uint32_t total_rows
     if (op == nullptr || op->data == nullptr || op->sf == nullptr) return fail(DG_ERR_SHAPE, "%s: null operand", name);
     if (op->bits != 8 && op->bits != 4) return fail(DG_ERR_SHAPE, "invalid bits %u", op->bits);
     if (op->gran_k != 32 && op->gran_k != 128) return fail(DG_ERR_SHAPE, "invalid gran_k %u", op->gran_k);
-    if (op->major_mn) return fail(op->bits == 4 ? DG_ERR_SHAPE : DG_ERR_UNSUPPORTED, "%s: only K-major operands are supported", name);
+    if (op->major_mn && op->bits == 4) return fail(DG_ERR_SHAPE, "%s: FP4 operands must be K-major", name);
     if (op->bits == 4 && (op->k % 128 != 0 || op->ld % 128 != 0)) return fail(DG_ERR_SHAPE, "FP4 k and ld must be multiples of 128");
     if (op->bits == 4 && op->gran_k != 32) return fail(DG_ERR_UNSUPPORTED, "FP4 operands need gran_k = 32");
     if (op->k == 0 || op->k % op->gran_k != 0) return fail(DG_ERR_SHAPE, "k (%u) must be a multiple of the SF granularity (%u)", op->k, op->gran_k);
+    if (op->major_mn) {
+        // (groups, k, ld) bytes: the rows of a group are contiguous, ld is the pitch between two k
+        const uint32_t g = groups ? groups : 1;
+        if (op->ld < total_rows / g) return fail(DG_ERR_SHAPE, "%s: MN-major ld (%u) smaller than the rows of a group (%u)", name, op->ld, total_rows / g);
+        if (op->ld % 16 != 0) return fail(DG_ERR_SHAPE, "%s: MN-major pitch %u bytes must be a multiple of 16", name, op->ld);
+        const size_t need = static_cast<size_t>(g) * op->k * op->ld;
+        if (op->data_len < need) return fail(DG_ERR_SHAPE, "data buffer too small: %zu < %zu", op->data_len, need);
+        const size_t sf_words = dg_sf_words(total_rows, op->k, op->gran_k, groups);
+        if (op->sf_len < sf_words) return fail(DG_ERR_SHAPE, "sf buffer too small: %zu < %zu", op->sf_len, sf_words);
+        return DG_OK;
+    }
     if (op->ld < op->k) return fail(DG_ERR_SHAPE, "%s: ld (%u) smaller than k (%u)", name, op->ld, op->k);
     const uint32_t row_bytes = op->bits == 4 ? op->ld / 2 : op->ld;
     if (row_bytes % 16 != 0) return fail(DG_ERR_SHAPE, "%s: row pitch %u bytes must be a multiple of 16", name, row_bytes);
@@ -575,6 +588,8 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         if (pr.n % 256 != 0) return fail(DG_ERR_SHAPE, "gate|up weights: rows per group (%u) must be 2 x a multiple of 128", pr.n);
     }
     if (e.accumulate && e.has_alpha) return fail(DG_ERR_SHAPE, "alpha and accumulation are mutually exclusive");
+    const bool any_mn = !pr.bf16 && (a->major_mn || b->major_mn);
+    if (any_mn && swiglu) return fail(DG_ERR_UNSUPPORTED, "the fused gate/up activation takes K-major operands");
     if (a->k != b->k) return fail(DG_ERR_SHAPE, "a.k (%u) != b.k (%u)", a->k, b->k);
     if (pr.m == 0 || pr.n == 0) return DG_OK;
     const bool contiguous = pr.type == DG_GEMM_M_GROUPED_CONTIGUOUS;
@@ -600,7 +615,8 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         return fail(DG_ERR_UNSUPPORTED, "the fused gate/up activation needs an mk alignment of at least 32");
 
     dg_desc desc = {pr.type, pr.m, pr.n, pr.k, pr.groups, pr.expected_m, a->bits, b->bits, a->gran_k, b->gran_k,
-                    static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms)};
+                    static_cast<uint32_t>(out->kind), static_cast<uint32_t>(ctx->num_sms), (!pr.bf16 && a->major_mn) ? 1u : 0u,
+                    (!pr.bf16 && b->major_mn) ? 1u : 0u};
     dg_config cfg;
     KernelPlan plan;
     rc = choose_config(&desc, e.accumulate ? 1u : 0u, &cfg, &plan);
@@ -646,11 +662,20 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         uint64_t strides[2] = {a_pitch, a_pitch * ka_rows};
         const uint32_t slab = mxf4 ? 256u : 128u;    // one 128-byte slab of K per TMA box
         uint32_t box[3] = {slab, dg::kBlockM, 1};
+        if (!pr.bf16 && ka->major_mn) {
+            // (groups, k, ld): rows innermost; a box is 128 rows x one slab of K
+            dims[0] = ka_rows; dims[1] = pr.k; strides[0] = ka->ld; strides[1] = static_cast<uint64_t>(ka->ld) * pr.k;
+            box[0] = 128; box[1] = slab;
+        }
         rc = encode_map(&maps[0], map_dtype(ka->bits), 3, ka->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
         if (rc) return rc;
         uint64_t bdims[3] = {pr.k, kb_rows, kb_groups};
         uint64_t bstrides[2] = {b_pitch, b_pitch * kb_rows};
         uint32_t bbox[3] = {slab, plan.umma_n / plan.ctas, 1};
+        if (!pr.bf16 && kb->major_mn) {
+            bdims[0] = kb_rows; bdims[1] = pr.k; bstrides[0] = kb->ld; bstrides[1] = static_cast<uint64_t>(kb->ld) * pr.k;
+            bbox[0] = 128; bbox[1] = slab;
+        }
         rc = encode_map(&maps[1], map_dtype(kb->bits), 3, kb->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
         if (rc) return rc;
     }
@@ -731,6 +756,8 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         p.stream_a = (once && swap) ? 1 : 0;
         p.stream_b = (once && !swap) ? 1 : 0;
     }
+    p.mn_a = (!pr.bf16 && ka->major_mn) ? 1 : 0;
+    p.mn_b = (!pr.bf16 && kb->major_mn) ? 1 : 0;
     p.accumulate = e.accumulate ? 1 : 0;
     p.tc_util = (e.tc_util == 0 || e.tc_util > 100) ? 100 : e.tc_util;      // 0 means "unset", as in ops_sm100.rs:518-522
     p.has_alpha = (e.has_alpha && splits == 1) ? 1 : 0;   // with K ranges summed by the second kernel alpha is applied there

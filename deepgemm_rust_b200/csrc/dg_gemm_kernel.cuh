@@ -81,6 +81,8 @@ struct GemmParams {
     uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
     uint32_t stream_a, stream_b;   // that operand is read from DRAM once by the whole launch (weights of a skinny or small-group
                                    // problem): its loads carry the L2 evict-first hint
+    uint32_t mn_a, mn_b;       // that operand is MN-major in memory ((k, ld) bytes, rows contiguous; e4m3 only): its tiles arrive as
+                               // boxes of 128 rows x 128 k and the UMMA descriptors walk them with the MN-major strides
     uint32_t tc_util;          // tensor-core duty cycle in percent (100: no pause); below 100 the UMMA warp idles after every k-block
                                // for (100 - tc_util) / tc_util times the k-block's tensor time (bf16_gemm_sm100.rs:358-371)
     float alpha;
@@ -265,7 +267,8 @@ struct Scheduler {
 // How often a scale word must be (re)loaded and how many words one k-block needs.
 //   block_k_elems = 128 (e4m3) or 256 (e2m1 pairs).  A word covers 4*gran elements.
 struct SfPlan {
-    uint32_t period;  // load on k-blocks where kb % period == 0
+    uint32_t period;  // load on k-blocks where kb % period == 0; a power of two (1, 2 or 4)
+    uint32_t shift;   // log2(period): the loops use masks and shifts instead of dividing by a run-time value every k-block
     uint32_t words;   // words per row per load
 };
 DG_DEVICE SfPlan sf_plan(uint32_t gran, uint32_t block_k_elems) {
@@ -273,6 +276,7 @@ DG_DEVICE SfPlan sf_plan(uint32_t gran, uint32_t block_k_elems) {
     SfPlan s;
     if (per_word >= block_k_elems) { s.period = per_word / block_k_elems; s.words = 1; }
     else { s.period = 1; s.words = block_k_elems / per_word; }
+    s.shift = 31 - __clz(s.period);
     return s;
 }
 
@@ -397,7 +401,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
                 // a scale word is loaded where it starts and, for a K range that begins inside a word, at the range's first k-block
-                bool need_a = kScaled && (kb % plan_a.period == 0 || kb == t.kb0), need_b = kScaled && (kb % plan_b.period == 0 || kb == t.kb0);
+                bool need_a = kScaled && ((kb & (plan_a.period - 1)) == 0 || kb == t.kb0), need_b = kScaled && ((kb & (plan_b.period - 1)) == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -409,9 +413,9 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_tx : 0u));
                         if (need_a)
                             tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, row_a,
-                                        static_cast<int32_t>(t.ga * p.sf_a_cols + kb / plan_a.period * plan_a.words));
+                                        static_cast<int32_t>(t.ga * p.sf_a_cols + (kb >> plan_a.shift) * plan_a.words));
                         if (need_b) {
-                            const int32_t sf_y = static_cast<int32_t>(t.gb * p.sf_b_cols + kb / plan_b.period * plan_b.words);
+                            const int32_t sf_y = static_cast<int32_t>(t.gb * p.sf_b_cols + (kb >> plan_b.shift) * plan_b.words);
                             tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0), sf_y);
                             if constexpr (kOut == kOutSwiGluFp8)
                                 tma_load_2d(smem_sfb + stage * sfb_bytes + block_n * 2, &tmap_sfb, bar_sf_raw + stage,
@@ -429,18 +433,27 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
                         uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
                         uint8_t* dst_b = smem_b + stage * b_bytes + h * b_half;
+                        // an MN-major operand comes as boxes of 128 rows (innermost) x one slab of K, 16 KB each, one box per 128 rows
                         if constexpr (kCtas == 1) {
-                            if (p.stream_a) tma_load_3d_hint(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
+                            if (p.mn_a) tma_load_3d(dst_a, &tmap_a, bar_full + stage, row_a, kx, static_cast<int32_t>(t.ga));
+                            else if (p.stream_a) tma_load_3d_hint(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
                             else tma_load_3d(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
-                            if (p.stream_b) tma_load_3d_hint(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
+                            if (p.mn_b) {
+                                for (uint32_t j = 0; j < load_n / 128; ++j)
+                                    tma_load_3d(dst_b + j * 16384, &tmap_b, bar_full + stage, row_b + static_cast<int32_t>(j * 128), kx, static_cast<int32_t>(t.gb));
+                            } else if (p.stream_b) tma_load_3d_hint(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
                             else tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
                         } else {
                             const uint32_t bar_addr = full_bar_leader + stage * 8;
                             if (load_a) {
-                                if (p.stream_a) tma_load_3d_2cta_hint(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
+                                if (p.mn_a) tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, row_a, kx, static_cast<int32_t>(t.ga));
+                                else if (p.stream_a) tma_load_3d_2cta_hint(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
                                 else tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
                             }
-                            if (p.stream_b) tma_load_3d_2cta_hint(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
+                            if (p.mn_b) {
+                                for (uint32_t j = 0; j < load_n / 128; ++j)
+                                    tma_load_3d_2cta(dst_b + j * 16384, &tmap_b, bar_addr, row_b + static_cast<int32_t>(j * 128), kx, static_cast<int32_t>(t.gb));
+                            } else if (p.stream_b) tma_load_3d_2cta_hint(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
                             else tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
                         }
                     }
@@ -470,10 +483,14 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + e * block_n;
                 const uint32_t n_tile = sched.umma_n(t, kCtas);
-                const uint32_t idesc = kScaled ? make_idesc_block_scaled(kBlockM * kCtas, n_tile, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b)
-                                               : make_idesc_bf16(kBlockM * kCtas, n_tile);
+                const uint32_t idesc = (kScaled ? make_idesc_block_scaled(kBlockM * kCtas, n_tile, kMXF4 ? 1u : p.fmt_a, kMXF4 ? 1u : p.fmt_b)
+                                                : make_idesc_bf16(kBlockM * kCtas, n_tile)) | (p.mn_a << 15) | (p.mn_b << 16);
+                // MN-major tiles: 8 k-rows of 128 row-bytes form a 1024-byte swizzle atom (stride byte offset), the next 128 rows
+                // lie one box (16 KB) further (leading byte offset), and one UMMA (32 k) advances by 32 x 128 bytes
+                const uint32_t a_lbo = p.mn_a ? 16384u : 0u, b_lbo = p.mn_b ? 16384u : 0u;
+                const uint32_t a_kstep = (p.mn_a ? 4096u : kUmmaKBytes) >> 4, b_kstep = (p.mn_b ? 4096u : kUmmaKBytes) >> 4;
                 for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                    bool need_a = kScaled && (kb % plan_a.period == 0 || kb == t.kb0), need_b = kScaled && (kb % plan_b.period == 0 || kb == t.kb0);
+                    bool need_a = kScaled && ((kb & (plan_a.period - 1)) == 0 || kb == t.kb0), need_b = kScaled && ((kb & (plan_b.period - 1)) == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                     if (p.debug_flags & 2) need_a = need_b = false;
 #endif
@@ -517,14 +534,14 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                             }
                             idescs[k] = idesc_with_sf_ids(idesc, a_id, b_id);
                         }
-                        const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes + h * a_half), 0, 1024, 2);
-                        const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes + h * b_half), 0, 1024, 2);
+                        const uint64_t a_desc = make_smem_desc(smem_u32(smem_a + stage * a_bytes + h * a_half), a_lbo, 1024, 2);
+                        const uint64_t b_desc = make_smem_desc(smem_u32(smem_b + stage * b_bytes + h * b_half), b_lbo, 1024, 2);
                         if (leader_lane) {
                             #pragma unroll
                             for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
                                 const uint32_t accumulate = (kb != t.kb0 || h != 0 || k != 0) ? 1u : 0u;
                                 if constexpr (kScaled)
-                                    umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idescs[k],
+                                    umma_block_scaled<kCtas, kMXF4>(d_tmem, a_desc + k * a_kstep, b_desc + k * b_kstep, idescs[k],
                                                                     a_cols[k], b_cols[k], accumulate);
                                 else
                                     umma_f16<kCtas>(d_tmem, a_desc + k * (kUmmaKBytes >> 4), b_desc + k * (kUmmaKBytes >> 4), idesc, accumulate);
@@ -575,7 +592,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         bool ok = true;
         while (ok && sched.next(t)) {
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                bool need_a = kScaled && (kb % plan_a.period == 0 || kb == t.kb0), need_b = kScaled && (kb % plan_b.period == 0 || kb == t.kb0);
+                bool need_a = kScaled && ((kb & (plan_a.period - 1)) == 0 || kb == t.kb0), need_b = kScaled && ((kb & (plan_b.period - 1)) == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif

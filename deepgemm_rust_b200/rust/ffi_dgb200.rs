@@ -77,6 +77,8 @@ pub struct RawDesc {
     pub gran_b: u32,
     pub cd_dtype: u32,
     pub num_sms: u32,
+    pub major_a_mn: u32,
+    pub major_b_mn: u32,
 }
 
 #[repr(C)]
@@ -577,6 +579,8 @@ pub struct Sm100Desc {
     pub gran_b: u32,
     pub cd_dtype: u32,
     pub num_sms: u32,
+    pub major_a_mn: bool,
+    pub major_b_mn: bool,
 }
 
 /// heuristics_sm100.rs:17-57, flattened: the same layout fields plus what this kernel adds (accumulator
@@ -605,6 +609,8 @@ pub fn best_config(desc: &Sm100Desc) -> Sm100Config {
         gran_b: desc.gran_b,
         cd_dtype: desc.cd_dtype,
         num_sms: desc.num_sms,
+        major_a_mn: desc.major_a_mn as u32,
+        major_b_mn: desc.major_b_mn as u32,
     };
     let mut cfg = RawConfig::default();
     check(unsafe { dg_best_config(&raw, &mut cfg) }).expect("no SM100 layout candidate");

@@ -55,7 +55,8 @@ typedef struct {
     uint32_t rows, k, ld;
     uint32_t bits;        /* 8 = e4m3, 4 = packed e2m1 */
     uint32_t gran_k;      /* 32 or 128 */
-    uint32_t major_mn;    /* must be 0: K-major operands only */
+    uint32_t major_mn;    /* 0: K-major, (rows, ld) with ld >= k.  1 (e4m3 only): MN-major, (k, ld) bytes per group with ld >= rows and
+                           * ld a multiple of 16: element (row r, k) at data[(group * k_total + k) * ld + r] (ops_sm100.rs:336-362) */
     size_t data_len;      /* bytes available at data */
     size_t sf_len;        /* words available at sf */
 } dg_lp_operand;
@@ -297,6 +298,7 @@ typedef struct {
     uint32_t gran_a, gran_b;
     uint32_t cd_dtype;   /* DG_OUT_* */
     uint32_t num_sms;
+    uint32_t major_a_mn, major_b_mn;   /* heuristics_sm100.rs:72-73 */
 } dg_desc;
 typedef struct {
     uint32_t swap_ab;            /* always 0: A rows ride the UMMA M dimension */
