@@ -347,9 +347,9 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < num_stages; ++s) {
-            mbar_init(bar_full + s, 1);
+            mbar_init(bar_full + s, 2);       // one arrival per producer warp (operand A, operand B)
             mbar_init(bar_empty + s, 1);
-            mbar_init(bar_sf_raw + s, 1);
+            mbar_init(bar_sf_raw + s, 2);
             mbar_init(bar_sf_ready + s, kCtas);
         }
         for (uint32_t e = 0; e < 2; ++e) {
@@ -383,14 +383,21 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     // instructions with lane 0: addresses and descriptors stay warp-uniform, so they live in
     // uniform registers instead of being moved there one by one for every tcgen05 / TMA
     // instruction (which alone costs ~190 cycles per UMMA).
-    if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
+    if (warp == 0 || warp == 3) {
+        // ------------------------------------------------------------ TMA producers
+        // Two warps, one per operand: warp 0 brings A and its scale words, warp 3 B and its scale words.  Issuing a stage's four
+        // to six loads from one lane took ~450 cycles per 128 bytes of K, more than the tensor pipe needs for them at N = 224;
+        // halved, the loads of a stage are on their way sooner after its buffer is released.  Both warps arrive on the stage's
+        // barriers (count 2), each with the bytes of its own operand.
+        const bool b_side = warp == 3;
         Scheduler sched(p, kCtas, kSwap, cluster_rank);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         const uint32_t full_bar_leader = kCtas == 2 ? mapa_u32(smem_u32(bar_full), leader_rank) : 0u;
         const uint64_t stream_policy = (p.stream_a | p.stream_b) ? l2_policy_evict_first() : 0ull;
+        const bool leader_lane = elect_one();      // the lane that issues; the same one for the whole kernel
+        const uint32_t a_tx = a_bytes >> p.tx_shift_a, b_tx = b_bytes >> p.tx_shift_b;
         while (ok && sched.next(t)) {
             const int32_t row_a = static_cast<int32_t>(t.m0 + cta_rank * kBlockM);
             // fused gate/up activation: rank 0 takes the gate rows [n0, n0 + load_n) of the group's B block, rank 1 the up rows
@@ -398,66 +405,80 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
             // rows from rank 0 and the second half from rank 1, so rank 1's box starts where that half starts.
             const int32_t row_b = static_cast<int32_t>(kOut == kOutSwiGluFp8 ? t.n0 + cta_rank * p.n
                                                        : (kSwap ? t.n0 + cta_rank * (sched.umma_n(t, kCtas) / 2) : t.n0 + cta_rank * load_n));
+            // a pair's second CTA whose 128 rows all lie past the end of the group (or of the matrix) loads no A rows: its
+            // accumulator rows are never stored, and the operand stream from L2 is what bounds these tiles
+            const bool load_a = kCtas == 1 || static_cast<uint32_t>(row_a) < t.m_end;
             for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
-                if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, 0x100 + stage)) { ok = false; break; }
+                if (!mbar_wait_warp(bar_empty + stage, phase ^ 1, abort_flag, p.status, (b_side ? 0x180 : 0x100) + stage)) { ok = false; break; }
                 // a scale word is loaded where it starts and, for a K range that begins inside a word, at the range's first k-block
                 bool need_a = kScaled && ((kb & (plan_a.period - 1)) == 0 || kb == t.kb0), need_b = kScaled && ((kb & (plan_b.period - 1)) == 0 || kb == t.kb0);
 #ifdef DG_PROFILE
                 if (p.debug_flags & 2) need_a = need_b = false;
 #endif
-                if (elect_one()) {
-                    if (need_a || need_b) {
-                        // fused gate/up activation: the scale words of the gate rows and of the up rows come as two boxes of
-                        // block_n / 2 words (one word per row and stage: per-128 scales only)
-                        const uint32_t sfb_tx = kOut == kOutSwiGluFp8 ? block_n * 4 : sfb_bytes;
-                        mbar_arrive_expect_tx(bar_sf_raw + stage, (need_a ? sfa_bytes : 0u) + (need_b ? sfb_tx : 0u));
-                        if (need_a)
-                            tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, row_a,
-                                        static_cast<int32_t>(t.ga * p.sf_a_cols + (kb >> plan_a.shift) * plan_a.words));
-                        if (need_b) {
-                            const int32_t sf_y = static_cast<int32_t>(t.gb * p.sf_b_cols + (kb >> plan_b.shift) * plan_b.words);
-                            tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0), sf_y);
-                            if constexpr (kOut == kOutSwiGluFp8)
-                                tma_load_2d(smem_sfb + stage * sfb_bytes + block_n * 2, &tmap_sfb, bar_sf_raw + stage,
-                                            static_cast<int32_t>(t.n0 + p.n), sf_y);
+                const uint32_t bar_addr = full_bar_leader + stage * 8;
+                if (!b_side) {
+                    if (leader_lane) {
+                        if (need_a || need_b) {
+                            mbar_arrive_expect_tx(bar_sf_raw + stage, need_a ? sfa_bytes : 0u);
+                            if (need_a)
+                                tma_load_2d(smem_sfa + stage * sfa_bytes, &tmap_sfa, bar_sf_raw + stage, row_a,
+                                            static_cast<int32_t>(t.ga * p.sf_a_cols + (kb >> plan_a.shift) * plan_a.words));
                         }
-                    }
-                    const uint32_t a_tx = a_bytes >> p.tx_shift_a, b_tx = b_bytes >> p.tx_shift_b;
-                    // a pair's second CTA whose 128 rows all lie past the end of the group (or of the matrix) loads no A rows: its
-                    // accumulator rows are never stored, and the operand stream from L2 is what bounds these tiles
-                    const bool load_a = kCtas == 1 || static_cast<uint32_t>(row_a) < t.m_end;
-                    if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, a_tx + b_tx);
-                    // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
-                    else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, (t.m0 + kBlockM < t.m_end ? 2u : 1u) * a_tx + 2 * b_tx);
-                    for (uint32_t h = 0; h < halves; ++h) {
-                        const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
-                        uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
-                        uint8_t* dst_b = smem_b + stage * b_bytes + h * b_half;
-                        // an MN-major operand comes as boxes of 128 rows (innermost) x one slab of K, 16 KB each, one box per 128 rows
-                        if constexpr (kCtas == 1) {
-                            if (p.mn_a) tma_load_3d(dst_a, &tmap_a, bar_full + stage, row_a, kx, static_cast<int32_t>(t.ga));
-                            else if (p.stream_a) tma_load_3d_hint(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
-                            else tma_load_3d(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
-                            if (p.mn_b) {
-                                for (uint32_t j = 0; j < load_n / 128; ++j)
-                                    tma_load_3d(dst_b + j * 16384, &tmap_b, bar_full + stage, row_b + static_cast<int32_t>(j * 128), kx, static_cast<int32_t>(t.gb));
-                            } else if (p.stream_b) tma_load_3d_hint(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
-                            else tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
-                        } else {
-                            const uint32_t bar_addr = full_bar_leader + stage * 8;
-                            if (load_a) {
+                        if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, a_tx);
+                        // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
+                        else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, (t.m0 + kBlockM < t.m_end ? 2u : 1u) * a_tx);
+                        for (uint32_t h = 0; h < halves; ++h) {
+                            const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
+                            uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
+                            // an MN-major operand comes as boxes of 128 rows (innermost) x one slab of K, 16 KB each, one box per 128 rows
+                            if constexpr (kCtas == 1) {
+                                if (p.mn_a) tma_load_3d(dst_a, &tmap_a, bar_full + stage, row_a, kx, static_cast<int32_t>(t.ga));
+                                else if (p.stream_a) tma_load_3d_hint(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
+                                else tma_load_3d(dst_a, &tmap_a, bar_full + stage, kx, row_a, static_cast<int32_t>(t.ga));
+                            } else if (load_a) {
                                 if (p.mn_a) tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, row_a, kx, static_cast<int32_t>(t.ga));
                                 else if (p.stream_a) tma_load_3d_2cta_hint(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga), stream_policy);
                                 else tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
                             }
-                            if (p.mn_b) {
-                                for (uint32_t j = 0; j < load_n / 128; ++j)
-                                    tma_load_3d_2cta(dst_b + j * 16384, &tmap_b, bar_addr, row_b + static_cast<int32_t>(j * 128), kx, static_cast<int32_t>(t.gb));
-                            } else if (p.stream_b) tma_load_3d_2cta_hint(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
-                            else tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
+                        }
+                    }
+                } else {
+                    if (leader_lane) {
+                        if (need_a || need_b) {
+                            // fused gate/up activation: the scale words of the gate rows and of the up rows come as two boxes of
+                            // block_n / 2 words (one word per row and stage: per-128 scales only)
+                            const uint32_t sfb_tx = kOut == kOutSwiGluFp8 ? block_n * 4 : sfb_bytes;
+                            mbar_arrive_expect_tx(bar_sf_raw + stage, need_b ? sfb_tx : 0u);
+                            if (need_b) {
+                                const int32_t sf_y = static_cast<int32_t>(t.gb * p.sf_b_cols + (kb >> plan_b.shift) * plan_b.words);
+                                tma_load_2d(smem_sfb + stage * sfb_bytes, &tmap_sfb, bar_sf_raw + stage, static_cast<int32_t>(t.n0), sf_y);
+                                if constexpr (kOut == kOutSwiGluFp8)
+                                    tma_load_2d(smem_sfb + stage * sfb_bytes + block_n * 2, &tmap_sfb, bar_sf_raw + stage,
+                                                static_cast<int32_t>(t.n0 + p.n), sf_y);
+                            }
+                        }
+                        if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, b_tx);
+                        else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * b_tx);
+                        for (uint32_t h = 0; h < halves; ++h) {
+                            const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
+                            uint8_t* dst_b = smem_b + stage * b_bytes + h * b_half;
+                            if constexpr (kCtas == 1) {
+                                if (p.mn_b) {
+                                    for (uint32_t j = 0; j < load_n / 128; ++j)
+                                        tma_load_3d(dst_b + j * 16384, &tmap_b, bar_full + stage, row_b + static_cast<int32_t>(j * 128), kx, static_cast<int32_t>(t.gb));
+                                } else if (p.stream_b) tma_load_3d_hint(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
+                                else tma_load_3d(dst_b, &tmap_b, bar_full + stage, kx, row_b, static_cast<int32_t>(t.gb));
+                            } else {
+                                if (p.mn_b) {
+                                    for (uint32_t j = 0; j < load_n / 128; ++j)
+                                        tma_load_3d_2cta(dst_b + j * 16384, &tmap_b, bar_addr, row_b + static_cast<int32_t>(j * 128), kx, static_cast<int32_t>(t.gb));
+                                } else if (p.stream_b) tma_load_3d_2cta_hint(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb), stream_policy);
+                                else tma_load_3d_2cta(dst_b, &tmap_b, bar_addr, kx, row_b, static_cast<int32_t>(t.gb));
+                            }
                         }
                     }
                 }
+                __syncwarp();
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
         }
