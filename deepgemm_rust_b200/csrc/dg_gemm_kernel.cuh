@@ -338,7 +338,6 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
     uint64_t* bar_full = bars;                       // A/B tiles of a stage landed (pair: both CTAs' tiles, on rank 0)
     uint64_t* bar_empty = bars + kMaxStages;         // the UMMAs reading a stage finished
     uint64_t* bar_sf_raw = bars + 2 * kMaxStages;    // scale words of a stage landed (per CTA)
-    uint64_t* bar_sf_ready = bars + 3 * kMaxStages;  // scale words re-ordered (pair: both CTAs, on rank 0)
     uint64_t* bar_tmem_full = bars + 4 * kMaxStages;
     uint64_t* bar_tmem_empty = bars + 4 * kMaxStages + 2;
     uint64_t* bar_tc = bars + 4 * kMaxStages + 4;     // the UMMAs of a k-block finished (only with a tensor-core duty cycle below 100 %)
@@ -347,10 +346,13 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < num_stages; ++s) {
-            mbar_init(bar_full + s, 2);       // one arrival per producer warp (operand A, operand B)
+            // a stage is ready for the UMMA warp when both producer warps have arrived (operand A, operand B; their bytes are
+            // counted on the same barrier) and, for the block-scaled kinds, the scale words of every CTA of the pair are in place:
+            // on the k-blocks that bring new scale words the re-ordering warp arrives when it is done, on the others the A-side
+            // producer arrives in its place, so the UMMA warp has one barrier to wait for per stage
+            mbar_init(bar_full + s, 2 + (kScaled ? kCtas : 0u));
             mbar_init(bar_empty + s, 1);
             mbar_init(bar_sf_raw + s, 2);
-            mbar_init(bar_sf_ready + s, kCtas);
         }
         for (uint32_t e = 0; e < 2; ++e) {
             mbar_init(bar_tmem_full + e, 1);
@@ -441,6 +443,11 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                                 else tma_load_3d_2cta(dst_a, &tmap_a, bar_addr, kx, row_a, static_cast<int32_t>(t.ga));
                             }
                         }
+                        if (kScaled && !(need_a || need_b)) {
+                            // no new scale words on this k-block: stand in for this CTA's re-ordering warp
+                            if constexpr (kCtas == 1) mbar_arrive(bar_full + stage);
+                            else mbar_arrive_remote(bar_full + stage, leader_rank);
+                        }
                     }
                 } else {
                     if (leader_lane) {
@@ -488,7 +495,7 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
         if (cta_rank == 0) {
             Scheduler sched(p, kCtas, kSwap, cluster_rank);
             Tile t;
-            uint32_t stage = 0, phase = 0, sf_phase_bits = 0, it = 0, tc_phase = 0;
+            uint32_t stage = 0, phase = 0, it = 0, tc_phase = 0;
             const uint32_t chunks_b = plan_b.words * (sf_block_n / 128);
             bool ok = true;
             const bool leader_lane = elect_one();      // the lane that issues; the same one for the whole kernel
@@ -520,10 +527,6 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     if (!mbar_wait_warp(bar_full + stage, phase, abort_flag, p.status, 0x300 + stage)) { ok = false; break; }
                     DG_PROF_ADD(1, t_full);
                     DG_PROF_T(t_sf);
-                    if (need_a || need_b) {
-                        if (!mbar_wait_warp(bar_sf_ready + stage, (sf_phase_bits >> stage) & 1, abort_flag, p.status, 0x400 + stage)) { ok = false; break; }
-                        sf_phase_bits ^= 1u << stage;
-                    }
                     DG_PROF_ADD(2, t_sf);
                     DG_PROF_T(t_issue);
                     tc_fence_after();
@@ -637,8 +640,8 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (kCtas == 1) mbar_arrive(bar_sf_ready + stage);
-                        else mbar_arrive_remote(bar_sf_ready + stage, leader_rank);
+                        if constexpr (kCtas == 1) mbar_arrive(bar_full + stage);
+                        else mbar_arrive_remote(bar_full + stage, leader_rank);
                     }
                 }
                 if (++stage == num_stages) stage = 0;

@@ -92,6 +92,14 @@ def test_heuristics_grouped_and_output_kinds():
     assert c.block_k in (128, 256)
     with pytest.raises(dg.DgError):
         dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 128, 128, a_bits=6, b_bits=4))
+    # MN-major operands (heuristics_sm100.rs:72-73): an MN-major B tile is whole 128-row boxes per CTA; FP4 must be K-major
+    for m, n, k in ((4096, 7168, 7168), (128, 2112, 7168), (300, 456, 1152)):
+        c = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, m, n, k, major_b_mn=True))
+        assert (c.block_n // c.cluster_m) % 128 == 0 and not c.swap_ab
+        c = dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, m, n, k, major_a_mn=True))
+        assert c.block_m == 128 * c.cluster_m and not c.swap_ab
+    with pytest.raises(dg.DgError):
+        dg.best_config(dg.Sm100Desc(dg.GemmType.Normal, 128, 128, 256, a_bits=8, b_bits=4, gran_b=32, major_b_mn=True))
 
 
 def test_no_device_fails_loudly():
