@@ -965,7 +965,7 @@ static int launch_f32scale(dg_ctx* ctx, uint32_t type, const uint8_t* a, uint32_
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(dg::kNumThreads, 1, 1);
+    cfg.blockDim = dim3(dg::kF32Threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];

@@ -6,17 +6,20 @@
 // scaling only takes power-of-two (UE8M0) scales, so an f32 scale with a mantissa cannot ride the UMMA: here every K block
 // is multiplied on its own (tcgen05.mma kind::f8f6f4 into one of two TMEM buffers, starting from zero) and the epilogue
 // warps fold it into f32 accumulators they keep in registers: acc += (block * sfa) * sfb, the reference's order of
-// operations.  One CTA per SM, 128 x 128 tiles: warp 0 loads A / B k-blocks with TMA, warp 1 issues the UMMAs, warps 4-7 own
-// 32 accumulator rows each, read every K block's partial tile (tcgen05.ld), scale and add it, and at the end store bf16
-// through swizzled staging and TMA.  Reading a 128 x 128 partial tile out of TMEM per 128 of K costs about three times the
-// tensor time of that block, so this path runs at roughly a third of the block-scaled kernel's rate: it exists for exactness
-// with arbitrary scales, the UE8M0 path for speed.
+// operations.  One 384-thread CTA per SM, 128 x 128 tiles: warp 0 loads A / B k-blocks with TMA, warp 1 issues the UMMAs, and
+// eight epilogue warps (4-11) each own 32 accumulator rows x 64 columns (a warp reads the TMEM lanes of its quadrant, warp % 4;
+// warps 4-7 take columns 0-63, warps 8-11 columns 64-127), read every K block's partial tile (tcgen05.ld), scale and add it,
+// and at the end store bf16 through swizzled staging and TMA.  Reading a partial tile out of TMEM per 128 of K costs more
+// than that block's tensor time even with eight warps, so this path stays well below the block-scaled kernel's rate: it
+// exists for exactness with arbitrary scales, the UE8M0 path for speed.
 #pragma once
 #include "dg_gemm_kernel.cuh"
 
 namespace dg {
 
 constexpr uint32_t kF32BlockN = 128;
+constexpr uint32_t kF32Threads = 384;      // producer, UMMA issuer, two idle warps, eight epilogue warps
+constexpr uint32_t kF32ColsPerWarp = 64;   // accumulator columns an epilogue warp keeps in registers
 
 struct F32ScaleParams {
     GemmParams g;              // shape, layout, scheduler inputs (block_n = tile_n = 128, block_k_elems = 128)
@@ -38,7 +41,7 @@ DG_DEVICE void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32
         : "memory");
 }
 
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kF32Threads, 1)
 dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_d) {
     const GemmParams& p = q.g;
@@ -52,7 +55,7 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem_a + num_stages * kTile;
     uint8_t* smem_epi = smem_b + num_stages * kTile;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + 8 * kEpiBuf);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + 16 * kEpiBuf);
     uint64_t* bar_full = bars;
     uint64_t* bar_empty = bars + kMaxStages;
     uint64_t* bar_tmem_full = bars + 2 * kMaxStages;         // a K block's partial tile is complete in TMEM buffer e
@@ -67,7 +70,7 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
         }
         for (uint32_t e = 0; e < 2; ++e) {
             mbar_init(bar_tmem_full + e, 1);
-            mbar_init(bar_tmem_empty + e, 4);
+            mbar_init(bar_tmem_empty + e, 8);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -135,8 +138,8 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
         __syncwarp();
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ epilogue
-        const uint32_t ew = warp - 4;
-        uint8_t* buf0 = smem_epi + ew * 2 * kEpiBuf;
+        const uint32_t ew = warp % 4, col_half = (warp - 4) / 4;       // TMEM lane quadrant; which 64 of the tile's 128 columns
+        uint8_t* buf0 = smem_epi + (warp - 4) * 2 * kEpiBuf;
         Scheduler sched(p, 1);
         Tile t;
         uint32_t block = 0, buf_idx = 0;
@@ -147,22 +150,22 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
             // the activation scale of this thread's row for K block kb, and the weight scale of the tile's 128 columns
             const float* sfa_row = q.sfa_t + static_cast<size_t>(t.ga) * total_kb * q.sfa_stride + row;
             const float* sfb_tile = q.sfb + (static_cast<size_t>(t.gb) * q.n_blocks128 + t.n0 / 128) * total_kb;
-            float acc[kF32BlockN];
+            float acc[kF32ColsPerWarp];
             #pragma unroll
-            for (uint32_t i = 0; i < kF32BlockN; ++i) acc[i] = 0.0f;
+            for (uint32_t i = 0; i < kF32ColsPerWarp; ++i) acc[i] = 0.0f;
             for (uint32_t kb = 0; kb < total_kb; ++kb, ++block) {
                 const uint32_t e = block & 1, buf_phase = (block >> 1) & 1;
                 const float sa = row_ok ? __ldg(sfa_row + static_cast<size_t>(kb) * q.sfa_stride) : 0.0f;
                 const float sb = __ldg(sfb_tile + kb);
                 if (!mbar_wait(bar_tmem_full + e, buf_phase, abort_flag, p.status, 0x600 + e)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t taddr = tmem_base + ((ew * 32) << 16) + e * kF32BlockN;
+                const uint32_t taddr = tmem_base + ((ew * 32) << 16) + e * kF32BlockN + col_half * kF32ColsPerWarp;
                 #pragma unroll
-                for (uint32_t c = 0; c < kF32BlockN / 32; ++c) {
+                for (uint32_t c = 0; c < kF32ColsPerWarp / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(taddr + c * 32, v);
                     tmem_ld_wait_x32(v);
-                    if (c + 1 == kF32BlockN / 32) {
+                    if (c + 1 == kF32ColsPerWarp / 32) {
                         // the buffer is in registers: hand it back to the UMMA warp
                         tc_fence_before();
                         __syncwarp();
@@ -177,7 +180,7 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
             // bf16 rows through 64-byte-swizzled staging, one TMA store per 32 columns (rows past the group's end are cut off by
             // the store's 32-row granularity exactly as in the block-scaled kernel)
             #pragma unroll
-            for (uint32_t c = 0; c < kF32BlockN / 32; ++c) {
+            for (uint32_t c = 0; c < kF32ColsPerWarp / 32; ++c) {
                 uint8_t* buf = buf0 + buf_idx * kEpiBuf;
                 if (lane == 0) tma_store_wait_read<1>();
                 __syncwarp();
@@ -191,7 +194,7 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
-                const uint32_t col0 = t.n0 + c * 32;
+                const uint32_t col0 = t.n0 + col_half * kF32ColsPerWarp + c * 32;
                 if (lane == 0) {
                     if (col0 < p.n && row0 < t.m_end) tma_store_3d(&tmap_d, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0), static_cast<int32_t>(t.gd));
                     tma_store_commit();
@@ -211,6 +214,6 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
     }
 }
 
-inline uint32_t f32scale_smem_bytes(uint32_t stages) { return 1024 + stages * 2 * kBlockM * kBlockKBytes + 8 * 2048 + (2 * kMaxStages + 4) * 8 + 16; }
+inline uint32_t f32scale_smem_bytes(uint32_t stages) { return 1024 + stages * 2 * kBlockM * kBlockKBytes + 16 * 2048 + (2 * kMaxStages + 4) * 8 + 16; }
 
 }  // namespace dg
