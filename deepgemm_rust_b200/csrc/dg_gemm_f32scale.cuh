@@ -171,9 +171,15 @@ dg_gemm_f32scale_kernel(const __grid_constant__ F32ScaleParams q, const __grid_c
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bar_tmem_empty + e);
                     }
+                    // two elements per instruction (packed f32x2: the same IEEE operations, half the issue slots)
+                    const float2 sa2 = make_float2(sa, sa), sb2 = make_float2(sb, sb);
                     #pragma unroll
-                    for (uint32_t i = 0; i < 32; ++i)
-                        acc[c * 32 + i] = __fadd_rn(acc[c * 32 + i], __fmul_rn(__fmul_rn(__uint_as_float(v[i]), sa), sb));
+                    for (uint32_t i = 0; i < 32; i += 2) {
+                        const float2 x = __fmul2_rn(__fmul2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sa2), sb2);
+                        const float2 r = __fadd2_rn(make_float2(acc[c * 32 + i], acc[c * 32 + i + 1]), x);
+                        acc[c * 32 + i] = r.x;
+                        acc[c * 32 + i + 1] = r.y;
+                    }
                 }
             }
             if (!ok) break;
