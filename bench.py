@@ -246,10 +246,11 @@ class DenseWork:
         self.launches = len(self.problems) + sum(1 for (m, n, k) in DENSE_SHAPES if dg.best_config(dg.Sm100Desc(0, m, n, k)).num_splits > 1)
         self.host = None
 
-    def step(self, record=None):
-        for p in self.problems:
+    def step(self, record=None, ctx=None, first=0, last=None):
+        """Launch problems [first, last) of the pass on `ctx` (default: the context the operands were made on)."""
+        for p in self.problems[first:last]:
             with _Phase(self.torch, record, "dense %dx%dx%d" % p["shape"]):
-                self.dg.fp8_fp4_gemm_dev(self.ctx, p["a"], p["b"], p["out"])
+                self.dg.fp8_fp4_gemm_dev(ctx or self.ctx, p["a"], p["b"], p["out"])
 
     def e2e_setup(self):
         """Weights (B and its scale words) are parameters: they stay resident in HBM, as in any caller of a GEMM library.  A step
@@ -332,6 +333,7 @@ class MoeWork:
         del x
         # rows travel through peer memory (kernels of the library) unless the peers cannot be mapped; every rank must agree
         self.peer, self.pipe, self.chunks, self.exchange_note = None, None, max(1, chunks), "nccl all_to_all_single"
+        self.before_combine = None
         self.fused_act = False
         if exchange == "peer":
             try:
@@ -435,6 +437,8 @@ class MoeWork:
             with self.phase("dispatch"):
                 a_op, ends = pe.dispatch(topi, xq, xsf)
             self.experts_compute(pe, a_op, ends)
+            if self.before_combine is not None:
+                self.before_combine()          # the dense GEMMs that run beside the combine are released here
             with self.phase("combine"):
                 return pe.combine(topw)
         plan = self.ep.plan(topi)
@@ -890,6 +894,9 @@ def main():
     ap.add_argument("--moe-chunks", type=int, default=1,
                     help="token micro-batches of the MoE step whose exchange overlaps the other micro-batches' GEMMs (measured slower "
                          "than 1 on 2 and 4 GPUs: the GEMMs lose more to the exchange kernels sharing their SMs than the overlap returns)")
+    ap.add_argument("--overlap-dense", type=int, default=1,
+                    help="default step: 1 (default) runs the dense GEMMs on a second stream beside the MoE layer's exchange kernels "
+                         "(measured +3 % at 1 and 2 GPUs), 0 runs the dense pass first and the MoE layer after it")
     ap.add_argument("--ep-blocks-per-sm", type=int, default=2, help="grid bound of the exchange kernels when they run beside the GEMMs")
     ap.add_argument("--fused-act", action="store_true",
                     help="MoE step: silu(gate)*up and its quantiser run in the gate/up GEMM's epilogue (output kind DG_OUT_SWIGLU_FP8) instead of "
@@ -939,7 +946,35 @@ def main():
     ctx.sync()
     record = {}
 
+    # --overlap-dense: the dense pass has no data in common with the MoE layer, so its GEMMs run on a second stream beside
+    # the layer's exchange kernels, which leave the tensor cores idle: the M = 128 GEMMs and the largest M = 4096 one beside
+    # route + dispatch, the other four beside the combine.  GEMM kernels of the two streams never share an SM (each needs
+    # most of its shared memory), so they simply take turns; the exchange kernels (two 256-thread blocks per SM) do.
+    overlap = bool(args.overlap_dense and dense is not None and moe is not None and moe.peer is not None and moe.pipe is None)
+    side = side_ctx = None
+    if overlap:
+        side = torch.cuda.Stream(device=dev)
+        side_ctx = dg.DgContext(local_rank, stream=side.cuda_stream)
+        order = sorted(range(len(dense.problems)), key=lambda i: (dense.problems[i]["shape"][0] != 128, dense.problems[i]["shape"] != (4096, 7168, 16384)))
+        dense.problems = [dense.problems[i] for i in order]      # M = 128 shapes, the largest GEMM, then the rest
+        n_first = 6
+
     def step(rec=None):
+        if overlap:
+            main = torch.cuda.current_stream(dev)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                dense.step(rec, side_ctx, 0, n_first)
+
+            def rest_of_dense():
+                side.wait_stream(main)                      # after the down GEMM has been queued
+                with torch.cuda.stream(side):
+                    dense.step(rec, side_ctx, n_first, None)
+            moe.record, moe.before_combine = rec, rest_of_dense
+            moe.step()
+            moe.record, moe.before_combine = None, None
+            main.wait_stream(side)
+            return
         if dense is not None:
             dense.step(rec)
         if moe is not None:
@@ -1012,9 +1047,17 @@ def main():
     parts = {}
     extra_launches = 0
     if dense is not None:
-        d_ms = timed(dense.step, args.steps) if moe is not None else ms_per_step
+        dense_rec = {}
+        d_ms = timed(lambda: dense.step(dense_rec), args.steps) if moe is not None else ms_per_step
         parts["dense_fp8"] = {"tflops": dense.flops * world / (d_ms * 1e-3) / 1e12, "ms_per_step": d_ms, "parallelism": "replica per GPU",
                               "launch_us_in_step_rank0": {k[6:]: round(v, 1) for k, v in launch_us.items() if k.startswith("dense ")}}
+        if overlap:
+            # on its own stream a dense launch queues behind the other stream's GEMMs: the events around it in the step measure
+            # that wait too, so the launch times used for the roofline come from the dense pass run on its own
+            parts["dense_fp8"]["launch_us_in_step_rank0_note"] = "includes time queued behind the MoE GEMMs of the other stream"
+            alone = phase_us(dense_rec)
+            parts["dense_fp8"]["launch_us_dense_pass_alone_rank0"] = {k[6:]: round(v, 1) for k, v in alone.items()}
+            launch_us.update(alone)
     if moe is not None:
         m_ms = timed(moe.step, args.steps) if dense is not None else ms_per_step
         gemm_ms, gemm_rows = moe.gate_up_alone()
@@ -1193,6 +1236,9 @@ def main():
                   "l2": "a step touches 1.1 GB of dense operands and 1.4-11 GB of expert weights per GPU, far more than the 126 MB L2"}
         if dense is not None:
             config["dense_shapes"] = DENSE_SHAPES
+        if overlap:
+            config["streams"] = ("the dense GEMMs run on a second stream beside the MoE layer's dispatch and combine kernels; both streams start "
+                                 "inside the step and are joined before it ends")
         if moe is not None:
             config["moe"] = dict(MOE, experts_per_gpu=moe.local_e, mk_alignment=128,
                                  collective=moe.exchange_note)
