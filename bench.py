@@ -1176,6 +1176,8 @@ def main():
                            "compute and downloads on three streams, ordered per buffer by events; the host side of the copies is shared by "
                            "all ranks of the node"}
     ctx.sync()
+    if side_ctx is not None:
+        side_ctx.sync()          # a device-side wait that ran out on the second stream is reported like one on the first
 
     if rank == 0:
         # ---- the launch with the largest share of this rank's step is the one the roofline entry describes
