@@ -1211,7 +1211,15 @@ def main():
         def roofline_entry(cand):
             us, name, fl, nbytes, kernel = cand
             row = launch_bound(fl, nbytes, us * 1e-6, peaks, 2)
-            keys = [key for key in traffic_table if name.startswith(key)]
+
+            def rows_match(entry):
+                # an entry measured (or scaled) for a given number of routed rows only describes launches within 5 % of it
+                want = entry.get("routed_rows")
+                if not want or "routed rows" not in name:
+                    return True
+                have = int(name.split(" routed rows")[0].split(", ")[-1])
+                return abs(have - want) <= 0.05 * want
+            keys = [key for key in traffic_table if name.startswith(key) and rows_match(traffic_table[key])]
             tr = traffic_table[max(keys, key=len)] if keys else None
             entry = {"bound": row["bound"], "kernel": kernel, "launch": name, "us_in_step": round(us, 1),
                      "share_of_step": round(us * 1e-3 / ms_per_step, 3), "sm_mhz_median": sm_mhz,
