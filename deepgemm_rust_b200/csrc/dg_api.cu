@@ -420,8 +420,8 @@ namespace {
 // ----------------------------------------------------------------------- tensor maps
 int encode_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base, const uint64_t* dims,
                const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle, const char* what) {
-    cuuint64_t gdim[3], gstride[2];
-    cuuint32_t gbox[3], estride[3] = {1, 1, 1};
+    cuuint64_t gdim[4], gstride[3];
+    cuuint32_t gbox[4], estride[4] = {1, 1, 1, 1};
     for (uint32_t i = 0; i < rank; ++i) { gdim[i] = dims[i]; gbox[i] = box[i]; }
     for (uint32_t i = 0; i + 1 < rank; ++i) gstride[i] = strides_bytes[i];
     if (reinterpret_cast<uintptr_t>(base) % 16 != 0) return fail(DG_ERR_SHAPE, "%s: base address must be 16-byte aligned", what);
@@ -651,6 +651,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
     const uint32_t sf_block_n = ceil_div(plan.umma_n, 128) * 128;
 
     CUtensorMap maps[5];
+    bool wide_k = false;
     {
         // packed e2m1 stays packed in shared memory for kind::mxf4 (16U4_ALIGN8B) and is expanded to one code per byte
         // for the mixed kind (16U4_ALIGN16B); dims and boxes of both are in logical 4-bit elements, pitches in bytes
@@ -667,6 +668,26 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
             dims[0] = ka_rows; dims[1] = pr.k; strides[0] = ka->ld; strides[1] = static_cast<uint64_t>(ka->ld) * pr.k;
             box[0] = 128; box[1] = slab;
         }
+        // Two-slab stages of plain K-major byte operands: the operand is described as (128 bytes, rows, K slabs, groups) so that one
+        // load brings both slabs of a stage (half as many TMA instructions per stage).  K must be whole slabs for that (a partial
+        // last slab would read into the next row), otherwise the 3-D maps and one load per slab stay.
+        const char* wide_env = getenv("DG_WIDE_K");
+        // (not where the loads carry the evict-first hint: dense problems of a single row block, see below)
+        const bool hinted = pr.type == DG_GEMM_NORMAL && pr.m <= (swap ? plan.umma_n : 128 * plan.ctas);
+        wide_k = plan.halves == 2 && !mxf4 && ka->bits == 8 && kb->bits == 8 && pr.k % 128 == 0 && !(!pr.bf16 && (ka->major_mn || kb->major_mn)) &&
+                 !hinted && !(wide_env && strcmp(wide_env, "0") == 0);
+        if (wide_k) {
+            uint64_t d4[4] = {128, ka_rows, pr.k / 128, ka_groups};
+            uint64_t s4[3] = {a_pitch, 128, a_pitch * ka_rows};
+            uint32_t b4[4] = {128, dg::kBlockM, 2, 1};
+            rc = encode_map(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, ka->data, d4, s4, b4, CU_TENSOR_MAP_SWIZZLE_128B, "A");
+            if (rc) return rc;
+            uint64_t e4[4] = {128, kb_rows, pr.k / 128, kb_groups};
+            uint64_t t4[3] = {b_pitch, 128, b_pitch * kb_rows};
+            uint32_t c4[4] = {128, plan.umma_n / plan.ctas, 2, 1};
+            rc = encode_map(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, kb->data, e4, t4, c4, CU_TENSOR_MAP_SWIZZLE_128B, "B");
+            if (rc) return rc;
+        } else {
         rc = encode_map(&maps[0], map_dtype(ka->bits), 3, ka->data, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, "A");
         if (rc) return rc;
         uint64_t bdims[3] = {pr.k, kb_rows, kb_groups};
@@ -678,6 +699,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         }
         rc = encode_map(&maps[1], map_dtype(kb->bits), 3, kb->data, bdims, bstrides, bbox, CU_TENSOR_MAP_SWIZZLE_128B, "B");
         if (rc) return rc;
+        }
     }
     const uint32_t sfa_cols = dg_sf_packed_cols(pr.k, ka->gran_k), sfb_cols = dg_sf_packed_cols(pr.k, kb->gran_k);
     {
@@ -756,6 +778,7 @@ int launch_gemm(dg_ctx* ctx, const dg_lp_operand* a, const dg_lp_operand* b, con
         p.stream_a = (once && swap) ? 1 : 0;
         p.stream_b = (once && !swap) ? 1 : 0;
     }
+    p.wide_k = wide_k ? 1 : 0;
     p.mn_a = (!pr.bf16 && ka->major_mn) ? 1 : 0;
     p.mn_b = (!pr.bf16 && kb->major_mn) ? 1 : 0;
     p.accumulate = e.accumulate ? 1 : 0;

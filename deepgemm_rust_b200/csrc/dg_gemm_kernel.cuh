@@ -81,6 +81,7 @@ struct GemmParams {
     uint32_t accumulate;       // D += A.B^T: tiles are added to the output with TMA reduce-add instead of stored
     uint32_t stream_a, stream_b;   // that operand is read from DRAM once by the whole launch (weights of a skinny or small-group
                                    // problem): its loads carry the L2 evict-first hint
+    uint32_t wide_k;           // both operand maps are 4-D (128 bytes, rows, K slabs, groups): one load brings the two K slabs of a stage
     uint32_t mn_a, mn_b;       // that operand is MN-major in memory ((k, ld) bytes, rows contiguous; e4m3 only): its tiles arrive as
                                // boxes of 128 rows x 128 k and the UMMA descriptors walk them with the MN-major strides
     uint32_t tc_util;          // tensor-core duty cycle in percent (100: no pause); below 100 the UMMA warp idles after every k-block
@@ -429,6 +430,11 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, a_tx);
                         // both CTAs' tiles complete on rank 0's barrier; rank 0 expects the bytes of the pair
                         else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, (t.m0 + kBlockM < t.m_end ? 2u : 1u) * a_tx);
+                        if (p.wide_k) {
+                            uint8_t* dst_a = smem_a + stage * a_bytes;
+                            if constexpr (kCtas == 1) tma_load_4d(dst_a, &tmap_a, bar_full + stage, 0, row_a, static_cast<int32_t>(kb * 2), static_cast<int32_t>(t.ga));
+                            else if (load_a) tma_load_4d_2cta(dst_a, &tmap_a, bar_addr, 0, row_a, static_cast<int32_t>(kb * 2), static_cast<int32_t>(t.ga));
+                        } else
                         for (uint32_t h = 0; h < halves; ++h) {
                             const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
                             uint8_t* dst_a = smem_a + stage * a_bytes + h * a_half;
@@ -466,6 +472,11 @@ dg_gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUt
                         }
                         if constexpr (kCtas == 1) mbar_arrive_expect_tx(bar_full + stage, b_tx);
                         else if (cta_rank == 0) mbar_arrive_expect_tx(bar_full + stage, 2 * b_tx);
+                        if (p.wide_k) {
+                            uint8_t* dst_b = smem_b + stage * b_bytes;
+                            if constexpr (kCtas == 1) tma_load_4d(dst_b, &tmap_b, bar_full + stage, 0, row_b, static_cast<int32_t>(kb * 2), static_cast<int32_t>(t.gb));
+                            else tma_load_4d_2cta(dst_b, &tmap_b, bar_addr, 0, row_b, static_cast<int32_t>(kb * 2), static_cast<int32_t>(t.gb));
+                        } else
                         for (uint32_t h = 0; h < halves; ++h) {
                             const int32_t kx = static_cast<int32_t>(kb * kBlockKElems + h * kHalfElems);
                             uint8_t* dst_b = smem_b + stage * b_bytes + h * b_half;

@@ -146,6 +146,22 @@ DG_DEVICE void tma_load_2d_2cta(void* smem, const void* tmap, uint32_t bar_clust
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y)
         : "memory");
 }
+// 4-D forms: the K-major operand seen as (128 bytes, rows, K slabs, groups), so that one instruction brings both K slabs
+// of a two-slab stage (x is always 0; slab and row coordinates have no alignment rule).
+DG_DEVICE void tma_load_4d(void* smem, const void* tmap, uint64_t* bar, int32_t x, int32_t y, int32_t z, int32_t w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+            smem_u32(smem)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
+DG_DEVICE void tma_load_4d_2cta(void* smem, const void* tmap, uint32_t bar_cluster_addr, int32_t x, int32_t y, int32_t z, int32_t w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(
+            smem_u32(smem)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+        : "memory");
+}
 // The same loads with an L2 eviction hint.  evict_first marks lines that will not be read again (an operand streamed
 // from DRAM exactly once): they leave L2 before anything else does, instead of pushing out lines that are still needed or
 // forcing write-backs of dirty ones; measured on B200, a streamed operand arrives 7-25 % faster with the hint.
