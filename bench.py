@@ -617,7 +617,23 @@ def run_config_table(args, torch, dg, ctx, dev, peaks):
     add(f"fp8 x fp4 {m}x{n}x{k}", t, 2.0 * m * n * k, m * k + n * k // 2 + 2 * m * n + sf_bytes(k, 32, m + n), tc8)
     t = timeit(lambda: dg.bf16_gemm_dev(ctx, x, k, m, w, k, n, k, out))
     add(f"bf16 {m}x{n}x{k}", t, 2.0 * m * n * k, 2 * (m + n) * k + 2 * m * n, 1e12 * peaks["bf16_tflops"])
-    del x, w, a4q, b4q, a8q, d
+    # the older f32-scale API on the same shape: exact per-K-block scaling (scales with mantissas) and the exponent-only route
+    a8u, b8u = (torch.randint(0, 120, (r, k), dtype=torch.uint8, device=dev) for r in (m, n))
+    sfa32 = torch.rand((m, k // 128), device=dev) + 0.5
+    sfb32 = torch.rand((n // 128, k // 128), device=dev) + 0.5
+    a_sf_t = dg.transform_sf_dev(ctx, sfa32, m, k // 128, 1)
+    nt = lambda: dg.fp8_gemm_nt_dev(ctx, dg.Fp8Tensor(a8u, m, k, k), a_sf_t, dg.Fp8Tensor(b8u, n, k, k), sfb32, d, n)
+    saved = os.environ.pop("DG_F32_SCALES", None)
+    t = timeit(nt)
+    add(f"fp8 {m}x{n}x{k}, f32 scales applied exactly per K block", t, 2.0 * m * n * k, (m + n) * k + 2 * m * n + 4 * (m + n // 128) * (k // 128), tc8)
+    os.environ["DG_F32_SCALES"] = "exponent"
+    t = timeit(nt)
+    add(f"fp8 {m}x{n}x{k}, f32 scales reduced to their exponents", t, 2.0 * m * n * k, (m + n) * k + 2 * m * n + 4 * (m + n // 128) * (k // 128), tc8)
+    if saved is None:
+        os.environ.pop("DG_F32_SCALES", None)
+    else:
+        os.environ["DG_F32_SCALES"] = saved
+    del x, w, a4q, b4q, a8q, d, a8u, b8u
     # quantisers
     for (r, c) in [(4096, 7168), (7168, 16384)]:
         src = randn(r, c)
