@@ -14,7 +14,7 @@ import torch
 
 import deepgemm_rust_b200 as dg
 from oracle import oracle as O
-from tests.helpers import sample_indices, to_f32
+from tests.helpers import dev, sample_indices, to_f32
 
 pytestmark = pytest.mark.gpu
 TOL, TIGHT_BF16, TIGHT_F32 = 1e-3, 2e-5, 1e-6
@@ -194,3 +194,50 @@ def test_c5_masked_decode_fp8_out_full_size(ctx):
         first_untouched = e * m_max + (int(mm[e]) + 255) // 256 * 256
         if first_untouched < (e + 1) * m_max:
             assert (got8[first_untouched:(e + 1) * m_max] == 0xAA).all()
+
+
+def test_dense_mn_major_full_size_equals_k_major(ctx):
+    # MN-major e4m3 operands at a benchmark shape: bit-identical to the K-major call on the same bytes, which the tests above
+    # hold to the oracle (every tile and k-block boundary of the 4096 x 7168 x 7168 problem is crossed)
+    m, n, k = 4096, 7168, 7168
+    gen = torch.Generator(device="cuda").manual_seed(77)
+    aq = torch.randint(0, 0x7E, (m, k), dtype=torch.uint8, device="cuda", generator=gen)
+    bq = torch.randint(0, 0x7E, (n, k), dtype=torch.uint8, device="cuda", generator=gen)
+    words = lambda rows: dg.sf_packed_cols(k, 128) * dg.sf_aligned_rows(rows)
+    asf = torch.randint(118, 130, (words(m) * 4,), dtype=torch.uint8, device="cuda", generator=gen).view(torch.int32)
+    bsf = torch.randint(118, 130, (words(n) * 4,), dtype=torch.uint8, device="cuda", generator=gen).view(torch.int32)
+    want = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_fp4_gemm_dev(ctx, dg.LpOperand(aq, asf, m, k, k), dg.LpOperand(bq, bsf, n, k, k), dg.Sm100Out.Bf16(want, n))
+    a_t = aq.t().contiguous()          # (k, m): rows contiguous
+    b_t = bq.t().contiguous()
+    for a_op, b_op in ((dg.LpOperand(a_t, asf, m, k, m, 8, 128, True), dg.LpOperand(bq, bsf, n, k, k)),
+                       (dg.LpOperand(aq, asf, m, k, k), dg.LpOperand(b_t, bsf, n, k, n, 8, 128, True)),
+                       (dg.LpOperand(a_t, asf, m, k, m, 8, 128, True), dg.LpOperand(b_t, bsf, n, k, n, 8, 128, True))):
+        d = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dg.fp8_fp4_gemm_dev(ctx, a_op, b_op, dg.Sm100Out.Bf16(d, n))
+        ctx.sync()
+        assert torch.equal(d, want)
+
+
+def test_f32_scale_gemm_full_size_sampled(ctx):
+    # the exact f32-scale route (ref_fp8_gemm_nt, reference.rs:85-114) at 4096 x 7168 x 7168 with scales that have mantissas:
+    # sampled rows x two 128-column blocks against the literal reference
+    m, n, k = 4096, 7168, 7168
+    rng = np.random.default_rng(5)
+    a = rng.integers(0, 0x7E, (m, k), dtype=np.uint8)
+    b = rng.integers(0, 0x7E, (n, k), dtype=np.uint8)
+    a[rng.random((m, k)) < 0.5] |= 0x80                       # both signs
+    sfa = (rng.random((m, k // 128), dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    sfb = (rng.random((n // 128, k // 128), dtype=np.float32) * 0.02 + 0.001).astype(np.float32)
+    a_sf_t = dg.transform_sf_dev(ctx, dev(sfa), m, k // 128, 1)
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+    dg.fp8_gemm_nt_dev(ctx, dg.Fp8Tensor(dev(a), m, k, k), a_sf_t, dg.Fp8Tensor(dev(b), n, k, k), dev(sfb), out, n)
+    ctx.sync()
+    rows = np.array(sorted(set(rng.integers(0, m, 40).tolist() + [0, 127, 128, 4095])), dtype=np.int64)
+    got = to_f32(out)
+    for blk in (0, 31, 55):
+        cols = np.arange(blk * 128, (blk + 1) * 128)
+        want = O.ref_fp8_gemm_nt(a[rows], sfa[rows], b[cols], sfb[blk:blk + 1], threads=8)
+        g = got[rows][:, cols]
+        assert np.max(np.abs(g - want) / np.maximum(np.abs(want), 1.0)) < 0.05          # tests/e2e.rs tolerance
+        assert O.calc_diff(g, want) <= 2e-5
